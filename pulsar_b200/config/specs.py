@@ -17,6 +17,7 @@ class NormSpec:
     size: int
     eps: float
     suffix: str = "weight"   # the weight's tensor name is the part's prefix + this ("" where the prefix is the whole name)
+    scalar: bool = False     # the weight is a single number (a tensor without dimensions) for all coordinates
 
 
 @dataclass(frozen=True)
@@ -56,6 +57,13 @@ class MixerSpec:
     values_from_keys: bool = False   # no v projection: the value is the key as projected (before rotation and norm)
     qk_norm_weight: bool = True      # False: q and k are divided by their root mean square (qk_norm_eps) without a weight
     qk_norm_after_rotation: bool = False   # the per-head norm of q and k follows the rotation instead of preceding it
+    # d: differential attention.  Every head has two score maps (its query and key rows hold [map 1 | map 2], head_dim
+    # each) over the same values; with a1, a2 their outputs the head gives unit_rms(a1 - lambda a2) * (1 - d), lambda =
+    # exp(<lq1, lk1>) - exp(<lq2, lk2>) + d from four learned vectors of head_dim (unit_rms: division by the root mean
+    # square over the head's values with ``norm_eps`` inside the root).  None: one map.
+    differential: Optional[float] = None
+    norm_eps: float = 0.0            # eps of norms inside the mixer (the differential form's norm of a head's output)
+    q_temperature: Optional[Tuple[float, int]] = None   # (coef, every): the query at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1)
     extra: Tuple[Tuple[str, object], ...] = ()   # free-form parameters of other kinds
 
     def option(self, name, default=None):
@@ -85,7 +93,8 @@ class FeedForwardSpec:
 class BlockSpec:
     """Arrangement of one layer.  ``kind`` "prenorm": x += mixer(norm1(x)); x += ffn(norm2(x)).
     ``kind`` "sandwich": x += post1(mixer(norm1(x))); x += post2(ffn(norm2(x))), the second sublayer only where
-    ``feed_forward`` is given."""
+    ``feed_forward`` is given.  ``kind`` "parallel": h = norm1(x); x += m * (mixer(shift(h)) + ffn(h)) with m =
+    ``residual_multiplier`` and shift the blend of neighbouring tokens where ``token_shift`` is set."""
     kind: str
     mixer: MixerSpec
     feed_forward: Optional[FeedForwardSpec]
@@ -95,6 +104,10 @@ class BlockSpec:
     names: Tuple[Tuple[str, str], ...] = ()  # sub-prefixes: mixer, feed_forward, mixer_norm, feed_forward_norm (+ the post norms)
     mixer_post_norm: Optional[NormSpec] = None          # norm of the mixer's output before it joins the stream
     feed_forward_post_norm: Optional[NormSpec] = None   # the same behind the feed-forward
+    residual_multiplier: float = 1.0                    # "parallel": what the sublayers' sum is multiplied by before it joins the stream
+    # "parallel": the mixer reads h_t + (h_(t-1) - h_t) * s with s a learned vector (tensor name under ``names``["shift"]) and
+    # h_(t-1) the norm's output for the token before (zeros before the first); the block keeps that row per sequence.
+    token_shift: bool = False
 
     def sub_prefix(self, part: str) -> str:
         return self.weight_prefix + dict(self.names)[part]
@@ -107,6 +120,7 @@ class LayerCall:
     (the later one then reads what the earlier one wrote: its mixer has own_kv False)."""
     block: int
     cache: int
+    state: Optional[int] = None      # a further cache entry, of kind "state", that belongs to the block itself (``Block.state_need``)
 
 
 @dataclass(frozen=True)
@@ -132,4 +146,6 @@ class ModelSpec:
 
     @property
     def n_cache_entries(self) -> int:
-        return 1 + max(call.cache for call in self.run_order) if self.run_order else 0
+        if not self.run_order:
+            return 0
+        return 1 + max(max(call.cache, -1 if call.state is None else call.state) for call in self.run_order)

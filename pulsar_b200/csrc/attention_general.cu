@@ -57,6 +57,7 @@ struct GeneralShape {
     float scale;
     int keep_first;     // keys below this stay visible whatever the window or chunk says; 0: none
     float softcap;      // > 0: scaled scores are capped to softcap * tanh(score / softcap)
+    int v_share;        // consecutive key heads that read one value head (the value pool has Hkv / v_share heads); 1: a value head per key head
 };
 
 // Tiles of 32 keys that a query (or a block of queries) with lowest key `lo` walks over: the tiles that hold kept first
@@ -144,7 +145,7 @@ paged_attention_general_kernel(const float* __restrict__ q, const T* __restrict_
             if (jj < lo && jj >= sh.keep_first) continue;      // uniform over the warp
             int page = table[jj / sh.page_size];
             if (!page_ok(page, bounds)) page = 0;
-            const T* vr = v_pool + (((size_t)page * sh.Hkv + g) * sh.page_size + jj % sh.page_size) * sh.v_stride;
+            const T* vr = v_pool + (((size_t)page * (sh.Hkv / sh.v_share) + g / sh.v_share) * sh.page_size + jj % sh.page_size) * sh.v_stride;
             const float pk = p_s[warp * 32 + kk];
 #pragma unroll
             for (int i = 0; i < ACC; ++i) {
@@ -327,8 +328,9 @@ general_tiled_kernel(const float* __restrict__ q, const T* __restrict__ k_pool, 
                 int page = table[j / sh.page_size];
                 if (!page_ok(page, bounds)) page = 0;
                 const size_t at = ((size_t)page * sh.Hkv + g) * sh.page_size + j % sh.page_size;
+                const size_t v_at = ((size_t)page * (sh.Hkv / sh.v_share) + g / sh.v_share) * sh.page_size + j % sh.page_size;
                 k_src = k_pool + at * sh.k_stride;
-                v_src = v_pool + at * sh.v_stride;
+                v_src = v_pool + v_at * sh.v_stride;
             }
             for (int part = sub; part < k_chunks; part += 4)
                 cp_async16(smem_u32(k_s + (size_t)key * ts.k_row + part * V), k_src + part * V, ok);
@@ -513,31 +515,35 @@ int dispatch_tiled(const float* q, const void* k_pool, const void* v_pool, void*
 #undef PB_TILED
 }
 
-// One warp per (token, head) of the fused projection row [q: Hq*Dk | k: Hkv*Dk | v: Hkv*Dv]:
-// queries to float32 [N, Hq, Dk], keys and values into the pages of the token's slot.
+// One warp per (token, head) of the fused projection row [q: Hq*Dk | k: Hk*Dk | v: Hv*Dv]:
+// queries to float32 [N, Hq, Dk], keys and values into the pages of the token's slot (pools of Hk and of Hv heads).
+// With temp_coef != 0 a query at position p is multiplied by 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1).
 template <typename T>
 __global__ void qkv_split_write_kernel(const T* __restrict__ qkv, float* __restrict__ q_out, T* __restrict__ k_pool,
-                                       T* __restrict__ v_pool, const int* __restrict__ slots, int Hq, int Hkv, int Dk, int Dv,
-                                       int page_size, const PoolBounds bounds) {
+                                       T* __restrict__ v_pool, const int* __restrict__ slots, int Hq, int Hk, int Hv, int Dk, int Dv,
+                                       int page_size, const int* __restrict__ positions, float temp_coef, int temp_every,
+                                       const PoolBounds bounds) {
     pdl_wait();         // may have come onto the SMs while the product before it was ending: nothing is touched before that one is done
     const int t = blockIdx.x, lane = threadIdx.x & 31;
     const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (head >= Hq + 2 * Hkv) return;
-    const size_t row = (size_t)Hq * Dk + (size_t)Hkv * (Dk + Dv);
+    if (head >= Hq + Hk + Hv) return;
+    const size_t row = (size_t)Hq * Dk + (size_t)Hk * Dk + (size_t)Hv * Dv;
     const T* base = qkv + (size_t)t * row;
     if (head < Hq) {
         const T* src = base + (size_t)head * Dk;
         float* dst = q_out + ((size_t)t * Hq + head) * Dk;
-        for (int i = lane; i < Dk; i += 32) dst[i] = to_float(src[i]);
+        float f = 1.0f;
+        if (temp_coef != 0.0f) f = 1.0f + temp_coef * logf((float)((positions[t] + 1) / temp_every + 1));
+        for (int i = lane; i < Dk; i += 32) dst[i] = to_float(src[i]) * f;
         return;
     }
     const int slot = slots[t];
     if (slot < 0 || !slot_ok(slot, page_size, bounds)) return;
-    const bool is_k = head < Hq + Hkv;
-    const int kvh = is_k ? head - Hq : head - Hq - Hkv;
-    const int D = is_k ? Dk : Dv;
-    const T* src = base + (size_t)Hq * Dk + (is_k ? (size_t)kvh * Dk : (size_t)Hkv * Dk + (size_t)kvh * Dv);
-    T* dst = (is_k ? k_pool : v_pool) + (((size_t)(slot / page_size) * Hkv + kvh) * page_size + slot % page_size) * D;
+    const bool is_k = head < Hq + Hk;
+    const int kvh = is_k ? head - Hq : head - Hq - Hk;
+    const int D = is_k ? Dk : Dv, Hp = is_k ? Hk : Hv;
+    const T* src = base + (size_t)Hq * Dk + (is_k ? (size_t)kvh * Dk : (size_t)Hk * Dk + (size_t)kvh * Dv);
+    T* dst = (is_k ? k_pool : v_pool) + (((size_t)(slot / page_size) * Hp + kvh) * page_size + slot % page_size) * D;
     for (int i = lane; i < D; i += 32) dst[i] = src[i];
 }
 
@@ -547,13 +553,13 @@ PB_EXPORT int pb_paged_attention_general(int dtype, const float* q, const void* 
                                          const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
                                          const int* seq_of_token, const float* slopes, int n_tokens, int Hq, int Hkv, int Dk,
                                          int Dv, int k_stride, int v_stride, int page_size, float scale, int window, int chunk,
-                                         int keep_first, float softcap, const float* sinks, cudaStream_t stream) {
+                                         int keep_first, float softcap, const float* sinks, int v_share, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (Dk <= 0 || Dv <= 0 || Dk > 4096 || Dv > 1024 || Hkv <= 0 || Hq <= 0 || Hq % Hkv || page_size <= 0 || k_stride < Dk ||
-        v_stride < Dv || window < 0 || chunk < 0 || keep_first < 0 || !(softcap >= 0.0f))
+        v_stride < Dv || window < 0 || chunk < 0 || keep_first < 0 || !(softcap >= 0.0f) || v_share <= 0 || Hkv % v_share)
         return PB_ERR_BAD_SIZE;
     if (Hq > 65535) return PB_ERR_TOO_LARGE;
-    GeneralShape sh{Hq, Hkv, Dk, Dv, k_stride, v_stride, page_size, window, chunk, table_stride, 0, scale, keep_first, softcap};
+    GeneralShape sh{Hq, Hkv, Dk, Dv, k_stride, v_stride, page_size, window, chunk, table_stride, 0, scale, keep_first, softcap, v_share};
     if (dtype == PB_F32)
         return dispatch_general<float>(q, k_pool, v_pool, out, block_table, cu_q, kv_len, seq_of_token, slopes, sinks, n_tokens, sh,
                                        stream);
@@ -564,28 +570,29 @@ PB_EXPORT int pb_paged_attention_general(int dtype, const float* q, const void* 
 }
 
 PB_EXPORT int pb_qkv_split_write(int dtype, const void* qkv, float* q_out, void* k_pool, void* v_pool, const int* slots,
-                                 int n_tokens, int Hq, int Hkv, int Dk, int Dv, int page_size, cudaStream_t stream) {
+                                 int n_tokens, int Hq, int Hk, int Hv, int Dk, int Dv, int page_size, const int* positions,
+                                 float temp_coef, int temp_every, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (Hq <= 0 || Hkv < 0 || Dk <= 0 || Dv <= 0 || page_size <= 0) return PB_ERR_BAD_SIZE;
-    const int heads = Hq + 2 * Hkv;
+    if (Hq <= 0 || Hk < 0 || Hv < 0 || Dk <= 0 || Dv <= 0 || page_size <= 0) return PB_ERR_BAD_SIZE;
+    if (temp_coef != 0.0f && (positions == nullptr || temp_every <= 0)) return PB_ERR_BAD_SIZE;
+    const int heads = Hq + Hk + Hv;
     dim3 grid(n_tokens, (heads + 3) / 4);
     if (dtype == PB_F32)
         launch_pdl(qkv_split_write_kernel<float>, grid, 128, 0, stream, (const float*)qkv, q_out, (float*)k_pool, (float*)v_pool, slots, Hq,
-                                                                Hkv, Dk, Dv, page_size, pb::pool_bounds_now());
+                                                                Hk, Hv, Dk, Dv, page_size, positions, temp_coef, temp_every, pb::pool_bounds_now());
     else if (dtype == PB_BF16)
         launch_pdl(qkv_split_write_kernel<__nv_bfloat16>, grid, 128, 0, stream, (const __nv_bfloat16*)qkv, q_out, (__nv_bfloat16*)k_pool,
-                                                                        (__nv_bfloat16*)v_pool, slots, Hq, Hkv, Dk, Dv, page_size,
-                                                                        pb::pool_bounds_now());
+                                                                        (__nv_bfloat16*)v_pool, slots, Hq, Hk, Hv, Dk, Dv, page_size,
+                                                                        positions, temp_coef, temp_every, pb::pool_bounds_now());
     else return PB_ERR_BAD_DTYPE;
     return launch_status();
 }
 
-// 1 when the tiled form takes these sizes (rows that are multiples of 16 bytes, value rows up to 512 wide), else 0.
 PB_EXPORT int pb_attention_general_tiled_supported(int dtype, const void* k_pool, const void* v_pool, int Hq, int Hkv, int Dk, int Dv,
                                                    int k_stride, int v_stride) {
     if (Dk <= 0 || Dv <= 0 || Dv > 512 || Hkv <= 0 || Hq <= 0 || Hq % Hkv || k_stride < Dk || v_stride < Dv) return 0;
     TiledShape ts{};
-    ts.g = GeneralShape{Hq, Hkv, Dk, Dv, k_stride, v_stride, 1, 0, 0, 0, 0, 1.0f, 0, 0.0f};
+    ts.g = GeneralShape{Hq, Hkv, Dk, Dv, k_stride, v_stride, 1, 0, 0, 0, 0, 1.0f, 0, 0.0f, 1};
     if (dtype == PB_F32) return tiled_shape<float>(ts, k_pool, v_pool) ? 1 : 0;
     if (dtype == PB_BF16) return tiled_shape<__nv_bfloat16>(ts, k_pool, v_pool) ? 1 : 0;
     return 0;
@@ -598,15 +605,16 @@ PB_EXPORT int pb_paged_attention_general_tiled(int dtype, const float* q, const 
                                                const int* kv_len, const float* slopes, int n_tokens, int n_seqs, int row_tiles,
                                                int n_splits, int Hq, int Hkv, int Dk, int Dv, int k_stride, int v_stride,
                                                int page_size, float scale, int window, int chunk, int keep_first, float softcap,
-                                               const float* sinks, cudaStream_t stream) {
+                                               const float* sinks, int v_share, cudaStream_t stream) {
     if (n_tokens <= 0 || row_tiles <= 0) return 0;
+    if (v_share <= 0 || Hkv % v_share) return PB_ERR_BAD_SIZE;
     if (!pb_attention_general_tiled_supported(dtype, k_pool, v_pool, Hq, Hkv, Dk, Dv, k_stride, v_stride)) return PB_ERR_BAD_SIZE;
     if (page_size <= 0 || window < 0 || chunk < 0 || keep_first < 0 || !(softcap >= 0.0f) || n_splits < 1 || n_splits > 65535 ||
         (n_splits > 1 && partial == nullptr) || (uintptr_t)q % 16)
         return PB_ERR_BAD_SIZE;
     if (Hkv > 65535) return PB_ERR_TOO_LARGE;
     TiledShape ts{};
-    ts.g = GeneralShape{Hq, Hkv, Dk, Dv, k_stride, v_stride, page_size, window, chunk, table_stride, 0, scale, keep_first, softcap};
+    ts.g = GeneralShape{Hq, Hkv, Dk, Dv, k_stride, v_stride, page_size, window, chunk, table_stride, 0, scale, keep_first, softcap, v_share};
     ts.n_seqs = n_seqs;
     ts.n_splits = n_splits;
     if (dtype == PB_F32) {

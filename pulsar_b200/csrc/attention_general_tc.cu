@@ -50,6 +50,7 @@ struct TcShape {
     float scale;
     int keep_first;
     float softcap;
+    int v_share;        // consecutive key heads that read one value head (the value pool has Hkv / v_share heads)
 };
 
 __device__ __forceinline__ int lowest_key(int pos, const TcShape& sh) {
@@ -111,7 +112,7 @@ general_tc_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pool, 
             if (!page_ok(page, bounds)) page = 0;
             const size_t at = ((size_t)page * sh.Hkv + kvh) * sh.page_size + key % sh.page_size;
             k_at = at * sh.k_stride;
-            v_at = at * sh.v_stride;
+            v_at = (((size_t)page * (sh.Hkv / sh.v_share) + kvh / sh.v_share) * sh.page_size + key % sh.page_size) * sh.v_stride;
         }
 #pragma unroll
         for (int c = sub; c < kChunksK; c += 4) cp_async16(k_dst + tile_offset<DK>(row, c), k_pool + k_at + c * 8, ok);
@@ -328,12 +329,13 @@ PB_EXPORT int pb_paged_attention_general_tc(int dtype, const float* q, const voi
                                             const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
                                             const float* slopes, int n_seqs, int n_q_tiles, int Hq, int Hkv, int Dk, int Dv,
                                             int k_stride, int v_stride, int page_size, float scale, int window, int chunk,
-                                            int keep_first, float softcap, const float* sinks, cudaStream_t stream) {
+                                            int keep_first, float softcap, const float* sinks, int v_share, cudaStream_t stream) {
     if (n_seqs <= 0 || n_q_tiles <= 0) return 0;
+    if (v_share <= 0 || Hkv % v_share) return PB_ERR_BAD_SIZE;
     if (!pb_attention_general_tc_supported(dtype, q, k_pool, v_pool, Hq, Hkv, Dk, Dv, k_stride, v_stride) || ((uintptr_t)out % 16))
         return PB_ERR_BAD_SIZE;
     if (page_size <= 0 || window < 0 || chunk < 0 || keep_first < 0 || !(softcap >= 0.0f)) return PB_ERR_BAD_SIZE;
-    const TcShape sh{n_seqs, Hq, Hkv, k_stride, v_stride, page_size, window, chunk, table_stride, scale, keep_first, softcap};
+    const TcShape sh{n_seqs, Hq, Hkv, k_stride, v_stride, page_size, window, chunk, table_stride, scale, keep_first, softcap, v_share};
     if (Dk == 64)
         return launch_general_tc<64, 64>(q, k_pool, v_pool, out, block_table, cu_q, kv_len, slopes, sinks, n_q_tiles, sh, stream);
     if (Dk == 128)

@@ -432,7 +432,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_grouped_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                             OutT* __restrict__ out, int N, int K, const GatedInter inter, int n_tiles, int w_rows,
                             const int* __restrict__ offsets, const int* __restrict__ tile_group,
-                            const int* __restrict__ tile_row0, const int* __restrict__ meta) {
+                            const int* __restrict__ tile_row0, const int* __restrict__ meta, const int* __restrict__ row_pair,
+                            const float* __restrict__ pair_scale) {
     const int m_tiles = meta[0];
     extern __shared__ unsigned char smem_raw[];
     // 128-byte swizzled tiles want 1024-byte alignment.
@@ -528,6 +529,8 @@ gemm_tcgen05_grouped_kernel(const __grid_constant__ CUtensorMap map_x, const __g
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int row = m0 + quarter * 32 + lane;
             const uint32_t lane_base = tmem_base + acc * kBN + ((uint32_t)(quarter * 32) << 16);
+            // a row's scale on the unit's input (a mixture whose weights multiply the experts' inputs): W (w x) = w (W x)
+            const float ws = (MODE == kSwiGLU && pair_scale != nullptr && row < M) ? pair_scale[row_pair[row]] : 1.0f;
             if (MODE == kSwiGLU) {
 #pragma unroll 1
                 for (int c = 0; c < kBN / 2; c += 32) {
@@ -537,7 +540,7 @@ gemm_tcgen05_grouped_kernel(const __grid_constant__ CUtensorMap map_x, const __g
                     float f[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        const float g = __uint_as_float(gv[i]), u = __uint_as_float(uv[i]);
+                        const float g = ws * __uint_as_float(gv[i]), u = ws * __uint_as_float(uv[i]);
                         f[i] = gated(g, u, inter);
                     }
                     if (row < M && n0 + c < inter) store32(out + (size_t)row * inter + n0 + c, f, inter - (n0 + c));
@@ -717,10 +720,13 @@ PB_EXPORT int pb_gemm_tcgen05(int mode, int out_dtype, const void* x, const void
 // matrices one behind the other, bfloat16.  mode 0: w_rows = N, out [P, N] (out_dtype bfloat16 or float32) = x W[group]^T.
 // mode 1: w_rows = 2 * inter (gate rows, then up rows), out [P, inter] bfloat16 = the gated unit (limit <= 0: none).
 // offsets [n_groups + 1], tile_group / tile_row0 [max_row_tiles], meta[0] = tiles listed: device arrays.
+// pair_scale (mode 1, or null): row r's gate and up sums are multiplied by pair_scale[row_pair[r]] before the gating.
 PB_EXPORT int pb_gemm_tcgen05_grouped(int mode, int out_dtype, const void* x, const void* w, void* out, int P, int N, int K,
                                       int n_groups, const int* offsets, const int* tile_group, const int* tile_row0, const int* meta,
-                                      int max_row_tiles, float limit, float alpha, float shift, cudaStream_t stream) {
+                                      int max_row_tiles, float limit, float alpha, float shift, const int* row_pair,
+                                      const float* pair_scale, cudaStream_t stream) {
     if (P <= 0 || max_row_tiles <= 0) return 0;
+    if (pair_scale != nullptr && row_pair == nullptr) return PB_ERR_BAD_SIZE;
     if (!pb_gemm_tcgen05_supported(mode, P, N, K) || n_groups <= 0 || (long long)n_groups * N > 0x7fffffff) return PB_ERR_BAD_SIZE;
     if ((((uintptr_t)x | (uintptr_t)w) & 15) != 0) return PB_ERR_BAD_SIZE;
     if (out_dtype != PB_BF16 && out_dtype != PB_F32) return PB_ERR_BAD_DTYPE;
@@ -740,7 +746,8 @@ PB_EXPORT int pb_gemm_tcgen05_grouped(int mode, int out_dtype, const void* x, co
         const long long tiles = (long long)max_row_tiles * (NT);                                                                  \
         const int grid = (int)(tiles < sm_count() ? tiles : sm_count());                                                          \
         gemm_tcgen05_grouped_kernel<MODE, OutT><<<grid, kThreads, kSmemBytes, stream>>>(mx, mw, (OutT*)out, N, K, INTER, NT, N,  \
-                                                                                        offsets, tile_group, tile_row0, meta);   \
+                                                                                        offsets, tile_group, tile_row0, meta,    \
+                                                                                        row_pair, pair_scale);                   \
         return launch_status();                                                                                                   \
     }
     if (mode == kSwiGLU) {

@@ -27,11 +27,12 @@ constexpr int kRouteTokens = 4;          // tokens a block of the router shares 
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, int* __restrict__ ids,
                                  float* __restrict__ weights, int n, int width, int n_experts, int top, float scale,
-                                 int renormalize) {
+                                 int renormalize, int n_extra, float* __restrict__ extra) {
     pdl_wait();
     extern __shared__ __align__(16) float smem[];
     float* x = smem;                                     // [kRouteTokens][width]
-    float* s = smem + (size_t)kRouteTokens * width;      // [kRouteTokens][n_experts]
+    float* s = smem + (size_t)kRouteTokens * width;      // [kRouteTokens][n_experts + n_extra]
+    const int n_rows = n_experts + n_extra;              // the rows behind the experts' compete for nothing: their sigmoids go to `extra`
     const int t0 = blockIdx.x * kRouteTokens, n_tok = min(kRouteTokens, n - t0);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     for (int i = threadIdx.x; i < kRouteTokens * width; i += blockDim.x) {
@@ -40,7 +41,7 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
     }
     __syncthreads();
     const bool vec = (width & 3) == 0 && ((uintptr_t)router & 15) == 0;
-    for (int e = warp; e < n_experts; e += warps) {
+    for (int e = warp; e < n_rows; e += warps) {
         const float* w = router + (size_t)e * width;
         float z[kRouteTokens];
 #pragma unroll
@@ -75,13 +76,14 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
 #pragma unroll
         for (int k = 0; k < kRouteTokens; ++k) {
             const float zk = warp_sum(z[k]);
-            if (lane == 0) s[k * n_experts + e] = 1.0f / (1.0f + expf(-zk));
+            if (lane == 0) s[k * n_rows + e] = 1.0f / (1.0f + expf(-zk));
         }
     }
     __syncthreads();
     if (warp >= n_tok) return;                           // warp k picks for token k of the block
-    float* sk = s + (size_t)warp * n_experts;
+    float* sk = s + (size_t)warp * n_rows;
     const size_t t = (size_t)t0 + warp;
+    for (int e = lane; e < n_extra; e += 32) extra[t * n_extra + e] = sk[n_experts + e];
     float total = 0.0f;
     for (int c = 0; c < top; ++c) {
         // the largest score left; among equals the lowest index
@@ -165,7 +167,8 @@ __device__ __forceinline__ float dot_row(const T* __restrict__ w, const float* _
 
 template <typename T>
 __global__ void moe_gate_up_kernel(const T* __restrict__ h, const T* __restrict__ w_gate_up, const int* __restrict__ ids,
-                                   T* __restrict__ act, int width, int ff, int top, const GatedInter p) {
+                                   T* __restrict__ act, int width, int ff, int top, const GatedInter p,
+                                   const float* __restrict__ in_weights) {
     pdl_wait();
     extern __shared__ __align__(16) float x[];             // [width]
     const int pair = blockIdx.x, t = pair / top;
@@ -173,18 +176,19 @@ __global__ void moe_gate_up_kernel(const T* __restrict__ h, const T* __restrict_
     for (int i = threadIdx.x; i < width; i += blockDim.x) x[i] = to_float(h[(size_t)t * width + i]);
     __syncthreads();
     const int e = ids[pair];
+    const float ws = in_weights ? in_weights[pair] : 1.0f;      // the pair's weight on the expert's input: W (w h) = w (W h)
     const T* w = w_gate_up + (size_t)e * 2 * ff * width;
     for (int j = blockIdx.y * warps + warp; j < ff; j += gridDim.y * warps) {
         const float g = dot_row(w + (size_t)j * width, x, width, lane);
         const float u = dot_row(w + (size_t)(ff + j) * width, x, width, lane);
-        if (lane == 0) act[(size_t)pair * ff + j] = from_float<T>(gated(g, u, p));
+        if (lane == 0) act[(size_t)pair * ff + j] = from_float<T>(gated(ws * g, ws * u, p));
     }
 }
 
 template <typename T>
 __global__ void moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const int* __restrict__ ids,
-                                const float* __restrict__ weights, const T* __restrict__ add, T* __restrict__ out, int width,
-                                int ff, int top) {
+                                const float* __restrict__ weights, const T* __restrict__ add, const float* __restrict__ add_scale,
+                                T* __restrict__ out, int width, int ff, int top) {
     pdl_wait();
     extern __shared__ __align__(16) float y[];             // [top][ff]
     const int t = blockIdx.x;
@@ -192,11 +196,11 @@ __global__ void moe_down_kernel(const T* __restrict__ act, const T* __restrict__
     for (int i = threadIdx.x; i < top * ff; i += blockDim.x) y[i] = to_float(act[(size_t)t * top * ff + i]);
     __syncthreads();
     for (int c = blockIdx.y * warps + warp; c < width; c += gridDim.y * warps) {
-        float sum = add ? to_float(add[(size_t)t * width + c]) : 0.0f;
+        float sum = add ? to_float(add[(size_t)t * width + c]) * (add_scale ? add_scale[t] : 1.0f) : 0.0f;
         for (int slot = 0; slot < top; ++slot) {
             const int e = ids[(size_t)t * top + slot];
             const float d = dot_row(w_down + ((size_t)e * width + c) * ff, y + (size_t)slot * ff, ff, lane);
-            sum = fmaf(weights[(size_t)t * top + slot], d, sum);
+            sum = fmaf(weights ? weights[(size_t)t * top + slot] : 1.0f, d, sum);
         }
         if (lane == 0) out[(size_t)t * width + c] = from_float<T>(sum);
     }
@@ -204,13 +208,14 @@ __global__ void moe_down_kernel(const T* __restrict__ act, const T* __restrict__
 
 }  // namespace
 
+// router [n_experts + n_extra, width]: the rows behind the experts' are scored too (sigmoid) and go to extra [n, n_extra].
 PB_EXPORT int pb_moe_route(int dtype, const void* h, const float* router, int* ids, float* weights, int n, int width, int n_experts,
-                           int top, float scale, int renormalize, cudaStream_t stream) {
+                           int top, float scale, int renormalize, int n_extra, float* extra, cudaStream_t stream) {
     if (n <= 0) return 0;
-    if (width <= 0 || n_experts <= 0 || top <= 0 || top > n_experts) return PB_ERR_BAD_SIZE;
-    const size_t smem = sizeof(float) * kRouteTokens * ((size_t)width + n_experts);
+    if (width <= 0 || n_experts <= 0 || top <= 0 || top > n_experts || n_extra < 0 || (n_extra > 0 && extra == nullptr)) return PB_ERR_BAD_SIZE;
+    const size_t smem = sizeof(float) * kRouteTokens * ((size_t)width + n_experts + n_extra);
     if (smem > 200 * 1024) return PB_ERR_TOO_LARGE;
-    int threads = 32 * n_experts;                        // a warp per expert where that fits a block
+    int threads = 32 * (n_experts + n_extra);             // a warp per row where that fits a block
     if (threads > 1024) threads = 1024;
     if (threads < 32 * kRouteTokens) threads = 32 * kRouteTokens;
     const int blocks = (n + kRouteTokens - 1) / kRouteTokens;
@@ -220,20 +225,21 @@ PB_EXPORT int pb_moe_route(int dtype, const void* h, const float* router, int* i
         if (smem > allowed) { ce = cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed = smem; }
         if (ce != cudaSuccess) return (int)ce;
         return launch_pdl(moe_route_kernel<float>, dim3(blocks), dim3(threads), smem, stream, (const float*)h, router, ids, weights, n,
-                          width, n_experts, top, scale, renormalize);
+                          width, n_experts, top, scale, renormalize, n_extra, extra);
     }
     if (dtype == PB_BF16) {
         static size_t allowed = 48 * 1024;
         if (smem > allowed) { ce = cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed = smem; }
         if (ce != cudaSuccess) return (int)ce;
         return launch_pdl(moe_route_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), smem, stream, (const __nv_bfloat16*)h, router, ids,
-                          weights, n, width, n_experts, top, scale, renormalize);
+                          weights, n, width, n_experts, top, scale, renormalize, n_extra, extra);
     }
     return PB_ERR_BAD_DTYPE;
 }
 
+// in_weights (float32 [n * top] or null): a pair's weight multiplies the expert's input instead of its output.
 PB_EXPORT int pb_moe_gate_up(int dtype, const void* h, const void* w_gate_up, const int* ids, void* act, int n, int width, int ff,
-                             int top, float limit, float alpha, float shift, cudaStream_t stream) {
+                             int top, float limit, float alpha, float shift, const float* in_weights, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (width <= 0 || ff <= 0 || top <= 0) return PB_ERR_BAD_SIZE;
     const size_t smem = sizeof(float) * (size_t)width;
@@ -245,15 +251,16 @@ PB_EXPORT int pb_moe_gate_up(int dtype, const void* h, const void* w_gate_up, co
     dim3 grid(n * top, by);
     if (dtype == PB_F32)
         return launch_pdl(moe_gate_up_kernel<float>, grid, dim3(warps * 32), smem, stream, (const float*)h, (const float*)w_gate_up, ids,
-                          (float*)act, width, ff, top, p);
+                          (float*)act, width, ff, top, p, in_weights);
     if (dtype == PB_BF16)
         return launch_pdl(moe_gate_up_kernel<__nv_bfloat16>, grid, dim3(warps * 32), smem, stream, (const __nv_bfloat16*)h,
-                          (const __nv_bfloat16*)w_gate_up, ids, (__nv_bfloat16*)act, width, ff, top, p);
+                          (const __nv_bfloat16*)w_gate_up, ids, (__nv_bfloat16*)act, width, ff, top, p, in_weights);
     return PB_ERR_BAD_DTYPE;
 }
 
+// weights null: every pair counts once (its weight went into the expert's input); add_scale (float32 [n] or null) multiplies `add`.
 PB_EXPORT int pb_moe_down(int dtype, const void* act, const void* w_down, const int* ids, const float* weights, const void* add,
-                          void* out, int n, int width, int ff, int top, cudaStream_t stream) {
+                          const float* add_scale, void* out, int n, int width, int ff, int top, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (width <= 0 || ff <= 0 || top <= 0) return PB_ERR_BAD_SIZE;
     const size_t smem = sizeof(float) * (size_t)top * ff;
@@ -264,9 +271,9 @@ PB_EXPORT int pb_moe_down(int dtype, const void* act, const void* w_down, const 
     dim3 grid(n, by);
     if (dtype == PB_F32)
         return launch_pdl(moe_down_kernel<float>, grid, dim3(warps * 32), smem, stream, (const float*)act, (const float*)w_down, ids,
-                          weights, (const float*)add, (float*)out, width, ff, top);
+                          weights, (const float*)add, add_scale, (float*)out, width, ff, top);
     if (dtype == PB_BF16)
         return launch_pdl(moe_down_kernel<__nv_bfloat16>, grid, dim3(warps * 32), smem, stream, (const __nv_bfloat16*)act,
-                          (const __nv_bfloat16*)w_down, ids, weights, (const __nv_bfloat16*)add, (__nv_bfloat16*)out, width, ff, top);
+                          (const __nv_bfloat16*)w_down, ids, weights, (const __nv_bfloat16*)add, add_scale, (__nv_bfloat16*)out, width, ff, top);
     return PB_ERR_BAD_DTYPE;
 }

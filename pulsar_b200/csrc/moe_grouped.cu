@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(kThreads)
 moe_grouped_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, const int* __restrict__ offsets,
                    const int* __restrict__ sorted, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                    const int* __restrict__ meta, bf16* __restrict__ act_out, float* __restrict__ y_out, int K, int n_out, int top,
-                   const GatedInter gating) {
+                   const GatedInter gating, const float* __restrict__ in_weights) {
     pdl_wait();
     constexpr int kWRows = MODE == 0 ? 2 * kBN : kBN;
     constexpr int kParts = MODE == 0 ? 2 : 1;              // gate and up, or one
@@ -171,11 +171,12 @@ moe_grouped_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, const
             if (r >= rows) continue;
             if (MODE == 0) {
                 bf16* dst = act_out + (size_t)(row0 + r) * n_out;
+                const float ws = in_weights ? in_weights[sorted[row0 + r]] : 1.0f;     // the pair's weight on the expert's input
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int col = n0 + warp_n * 32 + j * 8 + 2 * t;
-                    const float v0 = gated(acc[mi][j][2 * half], acc[mi][j + 4 * (kParts - 1)][2 * half], gating);
-                    const float v1 = gated(acc[mi][j][2 * half + 1], acc[mi][j + 4 * (kParts - 1)][2 * half + 1], gating);
+                    const float v0 = gated(ws * acc[mi][j][2 * half], ws * acc[mi][j + 4 * (kParts - 1)][2 * half], gating);
+                    const float v1 = gated(ws * acc[mi][j][2 * half + 1], ws * acc[mi][j + 4 * (kParts - 1)][2 * half + 1], gating);
                     if (col + 1 < n_out && (n_out & 1) == 0) *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(v0, v1);
                     else {
                         if (col < n_out) dst[col] = __float2bfloat16_rn(v0);
@@ -198,12 +199,14 @@ moe_grouped_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, const
 }
 
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, const float* __restrict__ weights,
-                                   const bf16* __restrict__ add, bf16* __restrict__ out, int width, int top, size_t total) {
+                                   const bf16* __restrict__ add, const float* __restrict__ add_scale, bf16* __restrict__ out, int width,
+                                   int top, size_t total) {
     pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t n = i / width, c = i % width;
-        float sum = add ? __bfloat162float(add[i]) : 0.0f;
-        for (int slot = 0; slot < top; ++slot) sum = fmaf(weights[n * top + slot], y[(size_t)place[n * top + slot] * width + c], sum);
+        float sum = add ? __bfloat162float(add[i]) * (add_scale ? add_scale[n] : 1.0f) : 0.0f;
+        for (int slot = 0; slot < top; ++slot)
+            sum = fmaf(weights ? weights[n * top + slot] : 1.0f, y[(size_t)place[n * top + slot] * width + c], sum);
         out[i] = __float2bfloat16_rn(sum);
     }
 }
@@ -227,12 +230,18 @@ PB_EXPORT int pb_moe_grouped_supported(int width, int ff, int n_experts) {
 // [n * top, width] scratch for the tcgen05 form, or null for the mma.sync form.
 PB_EXPORT int pb_gemm_tcgen05_grouped(int mode, int out_dtype, const void* x, const void* w, void* out, int P, int N, int K,
                                       int n_groups, const int* offsets, const int* tile_group, const int* tile_row0, const int* meta,
-                                      int max_row_tiles, float limit, float alpha, float shift, cudaStream_t stream);
+                                      int max_row_tiles, float limit, float alpha, float shift, const int* row_pair,
+                                      const float* pair_scale, cudaStream_t stream);
 
 PB_EXPORT int pb_moe_grouped(const void* h, const void* w_gate_up, const void* w_down, const int* ids, const float* weights,
                              const void* add, void* act, float* y, void* out, int* work, void* gathered, int n, int width, int ff,
-                             int n_experts, int top, float limit, float alpha, float shift, cudaStream_t stream) {
+                             int n_experts, int top, float limit, float alpha, float shift, int weight_input, const float* add_scale,
+                             cudaStream_t stream) {
     if (n <= 0) return 0;
+    // weight_input: a pair's weight multiplies its expert's input (in the gate/up epilogue: W (w h) = w (W h)) and the sum
+    // over a token's experts takes every pair once; add_scale (float32 [n] or null) multiplies `add`.
+    const float* in_weights = weight_input ? weights : nullptr;
+    const float* out_weights = weight_input ? nullptr : weights;
     if (!pb_moe_grouped_supported(width, ff, n_experts) || top <= 0 || top > n_experts) return PB_ERR_BAD_SIZE;
     const int pairs = n * top, tiles = (pairs + kBM - 1) / kBM + n_experts;
     if (tiles > 0x7fffffff / 2 || (ff + kBN - 1) / kBN > 65535 || (width + kBN - 1) / kBN > 65535) return PB_ERR_TOO_LARGE;
@@ -256,13 +265,13 @@ PB_EXPORT int pb_moe_grouped(const void* h, const void* w_gate_up, const void* w
                         width, top);
         if (rc != 0) return rc;
         rc = pb_gemm_tcgen05_grouped(1, PB_BF16, gathered, w_gate_up, act, pairs, 2 * ff, width, n_experts, offsets, tile_expert, tile_row0,
-                                     meta, tiles, limit, alpha, shift, stream);
+                                     meta, tiles, limit, alpha, shift, sorted, in_weights, stream);
         if (rc != 0) return rc;
         rc = pb_gemm_tcgen05_grouped(0, PB_F32, act, w_down, y, pairs, width, ff, n_experts, offsets, tile_expert, tile_row0, meta, tiles,
-                                     0.0f, 1.0f, 0.0f, stream);
+                                     0.0f, 1.0f, 0.0f, nullptr, nullptr, stream);
         if (rc != 0) return rc;
-        return launch_pdl(moe_combine_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)y, (const int*)place, weights,
-                          (const bf16*)add, (bf16*)out, width, top, total);
+        return launch_pdl(moe_combine_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)y, (const int*)place, out_weights,
+                          (const bf16*)add, add_scale, (bf16*)out, width, top, total);
     }
     const GatedInter gating(ff, limit > 0.0f ? limit : __builtin_huge_valf(), alpha, shift);
     constexpr int smem0 = kStages * (kBM + 2 * kBN) * kRow * 2, smem1 = kStages * (kBM + kBN) * kRow * 2;
@@ -275,12 +284,12 @@ PB_EXPORT int pb_moe_grouped(const void* h, const void* w_gate_up, const void* w
     }
     rc = launch_pdl(moe_grouped_kernel<0>, dim3(tiles, (ff + kBN - 1) / kBN), dim3(kThreads), smem0, stream, (const bf16*)h, (const bf16*)w_gate_up,
                     (const int*)offsets, (const int*)sorted, (const int*)tile_expert, (const int*)tile_row0, (const int*)meta, (bf16*)act,
-                    (float*)nullptr, width, ff, top, gating);
+                    (float*)nullptr, width, ff, top, gating, in_weights);
     if (rc != 0) return rc;
     rc = launch_pdl(moe_grouped_kernel<1>, dim3(tiles, (width + kBN - 1) / kBN), dim3(kThreads), smem1, stream, (const bf16*)act,
                     (const bf16*)w_down, (const int*)offsets, (const int*)sorted, (const int*)tile_expert, (const int*)tile_row0,
-                    (const int*)meta, (bf16*)nullptr, y, ff, width, top, gating);
+                    (const int*)meta, (bf16*)nullptr, y, ff, width, top, gating, (const float*)nullptr);
     if (rc != 0) return rc;
-    return launch_pdl(moe_combine_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)y, (const int*)place, weights,
-                      (const bf16*)add, (bf16*)out, width, top, total);
+    return launch_pdl(moe_combine_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)y, (const int*)place, out_weights,
+                      (const bf16*)add, add_scale, (bf16*)out, width, top, total);
 }

@@ -58,6 +58,15 @@ class DecoderModel(Part):
                     raise ValueError(f"cache entry {call.cache} is written by two layer calls")
                 if need != needs[call.cache]:
                     raise ValueError(f"cache entry {call.cache}: reader needs {need}, writer made {needs[call.cache]}")
+            if call.state is not None:
+                own = getattr(self.blocks[call.block], "state_need", lambda: None)()
+                if own is None or own.kind != "state":
+                    raise ValueError(f"run order gives block {call.block} a state entry, but the block keeps no state")
+                if needs[call.state] is not None:
+                    raise ValueError(f"cache entry {call.state} is used twice")
+                needs[call.state] = own
+            elif getattr(self.blocks[call.block], "state_need", lambda: None)() is not None:
+                raise ValueError(f"block {call.block} keeps state of its own: its entry of the run order must name a state entry")
         if any(n is None for n in needs):
             raise ValueError("run order leaves a cache entry unused")
         self._needs = needs
@@ -110,8 +119,14 @@ class DecoderModel(Part):
         for i, call in enumerate(s.run_order):
             following = self.blocks[s.run_order[i + 1].block] if i + 1 < len(s.run_order) else None
             ctx.next_norm = getattr(following, "mixer_norm", None)
+            ctx.next_block, ctx.next_call = following, (s.run_order[i + 1] if following is not None else None)
             ctx.has_following = following is not None
-            delta = self.blocks[call.block].forward(ctx, residual, delta, ctx.cache(call.cache))
+            view = ctx.cache(call.cache)
+            if call.state is not None:
+                view.block_state = ctx.cache(call.state).state
+            delta = self.blocks[call.block].forward(ctx, residual, delta, view)
+            if ctx.moved_residual is not None:
+                residual, ctx.moved_residual = ctx.moved_residual, None
             if ctx.on_layer is not None:
                 ctx.on_layer(i, residual, delta)
         rows = ctx.logit_rows

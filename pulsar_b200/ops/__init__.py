@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -84,13 +84,13 @@ _SIGNATURES = {
     "pb_sample": [_P, _I, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P],
     "pb_sample_workspace": [_I],
     "pb_argmax": [_P, _I, _I, _P, _P, _P],
-    "pb_paged_attention_general": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _P],
+    "pb_paged_attention_general": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _P],
     "pb_attention_general_tiled_supported": [_I, _P, _P, _I, _I, _I, _I, _I, _I],
-    "pb_paged_attention_general_tiled": [_I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _P],
+    "pb_paged_attention_general_tiled": [_I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _P],
     "pb_attention_general_tc_tile": [],
     "pb_attention_general_tc_supported": [_I, _P, _P, _P, _I, _I, _I, _I, _I, _I],
-    "pb_paged_attention_general_tc": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _P],
-    "pb_qkv_split_write": [_I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "pb_paged_attention_general_tc": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _P],
+    "pb_qkv_split_write": [_I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _F, _I, _P],
     "pb_heads_linear": [_I, _I, _P, _L, _I, _P, _P, _L, _I, _P, _L, _I, _I, _I, _I, _P],
     "pb_latent_prepare": [_I, _P, _L, _P, _L, _P, _F, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "pb_latent_expand_keys": [_I, _P, _P, _P, _I, _I, _I, _I, _P],
@@ -108,12 +108,18 @@ _SIGNATURES = {
     "pb_qk_prepare": [_I, _I, _P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "pb_sigmoid_gate_strided": [_I, _I, _P, _P, _L, _I, _I, _P],
     "pb_add_bias": [_I, _P, _P, _I, _I, _P],
-    "pb_moe_route": [_I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
-    "pb_moe_gate_up": [_I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _F, _P],
-    "pb_moe_down": [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "pb_moe_route": [_I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P],
+    "pb_moe_gate_up": [_I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _F, _P, _P],
+    "pb_moe_down": [_I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "pb_moe_grouped_workspace": [_I, _I, _I],
     "pb_moe_grouped_supported": [_I, _I, _I],
-    "pb_moe_grouped": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _F, _P],
+    "pb_moe_grouped": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _F, _I, _P, _P],
+    "pb_norm_shift": [_I, _P, _P, _F, _P, _P, _L, _P, _P, _P, _P, _P, _P, _I, _I, _P],
+    "pb_parallel_add": [_I, _P, _P, _P, _F, _P, _P, _P, _L, _P, _P, _P, _P, _F, _P, _P, _L, _P, _P, _P, _I, _I, _P],
+    "pb_activation": [_I, _I, _P, _P, ctypes.c_longlong, _I, _P],
+    "pb_min_gru_run": [],
+    "pb_min_gru": [_I, _P, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P],
+    "pb_diff_combine": [_I, _I, _P, _P, _I, _I, _I, _I, _F, _F, _F, _P],
 }
 _fns = {}
 # the entry points that launch kernels (the others answer questions on the host): what PULSAR_PROF=1 times
@@ -124,7 +130,8 @@ _LAUNCHERS = {"embed", "scale_cap", "move_ids", "add_rmsnorm", "rope_table", "qk
               "gemm_skinny_scaled", "gemm_tcgen05", "gemm_tcgen05_stream", "gemm_simt", "sample", "argmax", "table_update",
               "paged_attention_general", "paged_attention_general_tiled", "paged_attention_general_tc", "qkv_split_write", "heads_linear", "latent_prepare", "latent_expand_keys", "sigmoid_gate", "causal_conv_silu",
               "selective_scan", "selective_scan_prompt", "selective_scan_chunked", "post_norm_add", "clamped_glu",
-              "post_norm_add_bias", "glu_bias", "qk_prepare", "sigmoid_gate_strided", "add_bias", "moe_route", "moe_gate_up", "moe_down", "moe_grouped"}
+              "post_norm_add_bias", "glu_bias", "qk_prepare", "sigmoid_gate_strided", "add_bias", "moe_route", "moe_gate_up", "moe_down", "moe_grouped",
+              "norm_shift", "parallel_add", "activation", "min_gru", "diff_combine"}
 
 
 class KernelError(RuntimeError):
@@ -954,7 +961,7 @@ def paged_attention_general(ctx, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
                             slopes: Optional[torch.Tensor] = None, key_width: Optional[int] = None,
                             value_width: Optional[int] = None, tiled: Optional[bool] = None,
                             tensor_cores: Optional[bool] = None, keep_first: int = 0, softcap: Optional[float] = None,
-                            sinks: Optional[torch.Tensor] = None) -> None:
+                            sinks: Optional[torch.Tensor] = None, v_share: int = 1) -> None:
     """Attention of the step's tokens (``ctx``: cu_q, kv_len, seq_of_token, host.q_lens) with float32 queries ``q``
     [N, Hq, Dk] over pools [pages, Hkv, page, stride]: keys are the first ``key_width`` (default: all) elements of a
     ``k_pool`` row, values the first ``value_width`` of a ``v_pool`` row (the two may be one tensor).  ``slopes`` [Hq]
@@ -962,7 +969,9 @@ def paged_attention_general(ctx, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     ``keep_first`` keys of a sequence stay visible all the same.  ``softcap``: the scaled score becomes softcap *
     tanh(score / softcap).  ``sinks`` [Hq] float32: the softmax's denominator also holds exp(sinks[h]).
     ``tiled``: None picks the tiled kernel where it applies, False forces the plain one.  ``tensor_cores``: None picks the
-    tensor-core kernel for steps with portions where it applies, False never, True insists."""
+    tensor-core kernel for steps with portions where it applies, False never, True insists.
+    ``v_share``: that many consecutive key heads read one value head (``v_pool`` has Hkv / v_share heads): several score
+    maps over the same values."""
     _cuda(q, k_pool, v_pool, out, block_table, slopes, sinks)
     _check_against(k_pool)
     n, hq, dk = q.shape
@@ -972,7 +981,9 @@ def paged_attention_general(ctx, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     v_stride = v_pool.shape[3]
     dv = out.shape[2]
     assert q.dtype == torch.float32 and k_pool.dtype == v_pool.dtype == out.dtype and out.shape[:2] == (n, hq)
-    assert (key_width or k_stride) == dk and (value_width or v_stride) == dv and v_pool.shape[:3] == k_pool.shape[:3]
+    v_share = int(v_share)
+    assert (key_width or k_stride) == dk and (value_width or v_stride) == dv and v_share >= 1 and hkv % v_share == 0
+    assert v_pool.shape[:3] == (pages, hkv // v_share, page_size)
     assert block_table.dtype == torch.int32 and block_table.dim() == 2
     assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == hq)
     q_lens = ctx.host.q_lens
@@ -988,7 +999,7 @@ def paged_attention_general(ctx, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
             check(fn("pb_paged_attention_general_tc")(code(out.dtype), _p(q), _p(k_pool), _p(v_pool), _p(out), _p(block_table),
                                                       block_table.shape[1], _p(ctx.cu_q), _p(ctx.kv_len), _p(slopes), len(q_lens),
                                                       n_q_tiles, hq, hkv, dk, dv, k_stride, v_stride, page_size, float(scale),
-                                                      int(window or 0), int(chunk or 0), keep_first, softcap, _p(sinks), stream()),
+                                                      int(window or 0), int(chunk or 0), keep_first, softcap, _p(sinks), v_share, stream()),
                   "paged_attention_general_tc")
             return
         if insist:
@@ -1005,30 +1016,37 @@ def paged_attention_general(ctx, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
                                                      _p(block_table), block_table.shape[1], _p(ctx.cu_q), _p(ctx.kv_len),
                                                      _p(slopes), n, len(ctx.host.q_lens), row_tiles, n_splits, hq, hkv, dk, dv,
                                                      k_stride, v_stride, page_size, float(scale), int(window or 0),
-                                                     int(chunk or 0), keep_first, softcap, _p(sinks), stream()),
+                                                     int(chunk or 0), keep_first, softcap, _p(sinks), v_share, stream()),
               "paged_attention_general_tiled", kernels=2 if n_splits > 1 else 1)
         return
     check(fn("pb_paged_attention_general")(code(out.dtype), _p(q), _p(k_pool), _p(v_pool), _p(out), _p(block_table),
                                            block_table.shape[1], _p(ctx.cu_q), _p(ctx.kv_len), _p(ctx.seq_of_token), _p(slopes),
                                            n, hq, hkv, dk, dv, k_stride, v_stride, page_size, float(scale), int(window or 0),
-                                           int(chunk or 0), keep_first, softcap, _p(sinks), stream()), "paged_attention_general")
+                                           int(chunk or 0), keep_first, softcap, _p(sinks), v_share, stream()), "paged_attention_general")
 
 
 def qkv_split_write(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
                     slots: Optional[torch.Tensor], n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int,
-                    page_size: int) -> None:
-    """Split the fused projection rows [q: Hq*Dk | k: Hkv*Dk | v: Hkv*Dv]: queries to float32 ``q_out`` [N, Hq, Dk], keys and
-    values into their pages (``n_kv_heads`` 0: the row holds q only)."""
-    _cuda(qkv, q_out, k_pool, v_pool, slots)
+                    page_size: int, n_value_heads: Optional[int] = None, positions: Optional[torch.Tensor] = None,
+                    q_temperature: Optional[Tuple[float, int]] = None) -> None:
+    """Split the fused projection rows [q: Hq*Dk | k: Hk*Dk | v: Hv*Dv]: queries to float32 ``q_out`` [N, Hq, Dk], keys and
+    values into their pages (``n_kv_heads`` 0: the row holds q only; ``n_value_heads``: Hv where it is not Hk).
+    ``q_temperature`` = (coef, every): the query at position p (``positions`` int32 [N]) is multiplied by
+    1 + coef * ln(floor((p + 1) / every) + 1)."""
+    _cuda(qkv, q_out, k_pool, v_pool, slots, positions)
     _check_against(k_pool)
     n = qkv.shape[0]
-    assert qkv.shape[1] == n_heads * key_dim + n_kv_heads * (key_dim + value_dim) and q_out.dtype == torch.float32
+    n_v = n_kv_heads if n_value_heads is None else int(n_value_heads)
+    assert qkv.shape[1] == (n_heads + n_kv_heads) * key_dim + n_v * value_dim and q_out.dtype == torch.float32
     assert q_out.shape == (n, n_heads, key_dim)
     if n_kv_heads:
         assert k_pool.dtype == qkv.dtype and v_pool.dtype == qkv.dtype and slots.dtype == torch.int32
-        assert k_pool.shape[1:] == (n_kv_heads, page_size, key_dim) and v_pool.shape[1:] == (n_kv_heads, page_size, value_dim)
+        assert k_pool.shape[1:] == (n_kv_heads, page_size, key_dim) and v_pool.shape[1:] == (n_v, page_size, value_dim)
+    coef, every = (0.0, 1) if q_temperature is None else (float(q_temperature[0]), int(q_temperature[1]))
+    if coef != 0.0:
+        assert positions is not None and positions.dtype == torch.int32 and positions.numel() == n and every > 0
     check(fn("pb_qkv_split_write")(code(qkv.dtype), _p(qkv), _p(q_out), _p(k_pool), _p(v_pool), _p(slots), n, n_heads, n_kv_heads,
-                                   key_dim, value_dim, page_size, stream()), "qkv_split_write")
+                                   n_v, key_dim, value_dim, page_size, _p(positions), coef, every, stream()), "qkv_split_write")
 
 
 def heads_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None) -> None:
@@ -1264,45 +1282,54 @@ def add_bias(x: torch.Tensor, bias: torch.Tensor) -> None:
 
 # ---------------------------------------------------------------- mixture of experts
 def moe_route(h: torch.Tensor, router: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, scale: float = 1.0,
-              renormalize: bool = False) -> None:
+              renormalize: bool = False, extra: Optional[torch.Tensor] = None) -> None:
     """ids [N, top] int32 and weights [N, top] float32 of the ``top`` largest sigmoid(router @ h) per token (float32 sums;
-    ties go to the lower index), weights times ``scale`` (after division by their sum with ``renormalize``)."""
-    _cuda(h, router, ids, weights)
+    ties go to the lower index), weights times ``scale`` (after division by their sum with ``renormalize``).  With ``extra``
+    (float32 [N, X]) the router has X more rows behind the experts' that compete for nothing: their sigmoids go there."""
+    _cuda(h, router, ids, weights, extra)
     n, width = h.shape
-    e = router.shape[0]
+    n_extra = 0 if extra is None else extra.shape[1]
+    e = router.shape[0] - n_extra
     top = ids.shape[1]
-    assert router.dtype == torch.float32 and router.shape == (e, width) and ids.dtype == torch.int32 and ids.shape == (n, top)
+    assert router.dtype == torch.float32 and router.shape == (e + n_extra, width) and ids.dtype == torch.int32 and ids.shape == (n, top)
     assert weights.dtype == torch.float32 and weights.shape == (n, top)
+    assert extra is None or (extra.dtype == torch.float32 and extra.shape == (n, n_extra))
     check(fn("pb_moe_route")(code(h.dtype), _p(h), _p(router), _p(ids), _p(weights), n, width, e, top, float(scale),
-                             1 if renormalize else 0, stream()), "moe_route")
+                             1 if renormalize else 0, n_extra, _p(extra), stream()), "moe_route")
 
 
-def moe_gate_up(h: torch.Tensor, w_gate_up: torch.Tensor, ids: torch.Tensor, act: torch.Tensor, gating) -> None:
+def moe_gate_up(h: torch.Tensor, w_gate_up: torch.Tensor, ids: torch.Tensor, act: torch.Tensor, gating,
+                in_weights: Optional[torch.Tensor] = None) -> None:
     """act [N * top, ff] = the gated unit (``gating`` = (limit, alpha, shift) as in ``gated_linear``; None: SwiGLU) of every
-    token's chosen experts; ``w_gate_up`` [E, 2 ff, width] holds an expert's gate rows, then its up rows."""
-    _cuda(h, w_gate_up, ids, act)
+    token's chosen experts; ``w_gate_up`` [E, 2 ff, width] holds an expert's gate rows, then its up rows.  ``in_weights``
+    (float32 [N, top]): the expert reads weight * h (applied to the gate and up sums in float32: W (w h) = w (W h))."""
+    _cuda(h, w_gate_up, ids, act, in_weights)
     n, width = h.shape
     e, two_ff, w2 = w_gate_up.shape
     top = ids.shape[1]
     assert w2 == width and two_ff % 2 == 0 and act.shape == (n * top, two_ff // 2) and h.dtype == w_gate_up.dtype == act.dtype
     assert ids.dtype == torch.int32 and ids.shape[0] == n
+    assert in_weights is None or (in_weights.dtype == torch.float32 and in_weights.shape == (n, top))
     limit, alpha, shift = gating if gating is not None else (0.0, 1.0, 0.0)
     check(fn("pb_moe_gate_up")(code(h.dtype), _p(h), _p(w_gate_up), _p(ids), _p(act), n, width, two_ff // 2, top, float(limit),
-                               float(alpha), float(shift), stream()), "moe_gate_up")
+                               float(alpha), float(shift), _p(in_weights), stream()), "moe_gate_up")
 
 
-def moe_down(act: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, add: Optional[torch.Tensor],
-             out: torch.Tensor) -> None:
-    """out [N, width] = add + sum over a token's chosen experts, in the order of ``ids``, of weight * (w_down[e] @ act row)."""
-    _cuda(act, w_down, ids, weights, add, out)
+def moe_down(act: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: Optional[torch.Tensor], add: Optional[torch.Tensor],
+             out: torch.Tensor, add_scale: Optional[torch.Tensor] = None) -> None:
+    """out [N, width] = add * add_scale + sum over a token's chosen experts, in the order of ``ids``, of weight * (w_down[e] @
+    act row).  ``weights`` None: every pair counts once; ``add_scale`` (float32 [N]) None: 1."""
+    _cuda(act, w_down, ids, weights, add, out, add_scale)
     n, width = out.shape
     e, w2, ff = w_down.shape
     top = ids.shape[1]
     assert w2 == width and act.shape == (n * top, ff) and act.dtype == w_down.dtype == out.dtype
-    assert ids.dtype == torch.int32 and weights.dtype == torch.float32 and ids.shape == weights.shape == (n, top)
+    assert ids.dtype == torch.int32 and ids.shape == (n, top)
+    assert weights is None or (weights.dtype == torch.float32 and weights.shape == (n, top))
     assert add is None or (add.shape == out.shape and add.dtype == out.dtype)
-    check(fn("pb_moe_down")(code(out.dtype), _p(act), _p(w_down), _p(ids), _p(weights), _p(add), _p(out), n, width, ff, top, stream()),
-          "moe_down")
+    assert add_scale is None or (add_scale.dtype == torch.float32 and add_scale.numel() == n)
+    check(fn("pb_moe_down")(code(out.dtype), _p(act), _p(w_down), _p(ids), _p(weights), _p(add), _p(add_scale), _p(out), n, width, ff,
+                            top, stream()), "moe_down")
 
 
 # Steps of more than MOE_GROUPED_MIN tokens (bfloat16) sort their (token, expert) pairs by expert on the device and run every
@@ -1329,12 +1356,16 @@ def moe_grouped_workspace(n: int, top: int, n_experts: int) -> int:
 
 def moe_grouped(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
                 add: Optional[torch.Tensor], act: torch.Tensor, y: torch.Tensor, out: torch.Tensor, work: torch.Tensor, gating,
-                gathered: Optional[torch.Tensor] = None) -> None:
+                gathered: Optional[torch.Tensor] = None, weight_input: bool = False,
+                add_scale: Optional[torch.Tensor] = None) -> None:
     """What ``moe_gate_up`` and ``moe_down`` compute together, for steps of many tokens (bfloat16): pairs sorted by expert, the
     experts' products in tensor-core tiles, the weighted sum in the order of ``ids``.  ``act`` [N * top, ff] bfloat16, ``y``
     [N * top, width] float32 and ``work`` (int32, ``moe_grouped_workspace`` elements) are scratch.  With ``gathered``
-    (bfloat16 [N * top, width] scratch) the products run on the grouped tcgen05 kernel, else on mma.sync."""
-    _cuda(h, w_gate_up, w_down, ids, weights, add, act, y, out, work, gathered)
+    (bfloat16 [N * top, width] scratch) the products run on the grouped tcgen05 kernel, else on mma.sync.  ``weight_input``: a
+    pair's weight multiplies its expert's input (inside the gate/up epilogue) instead of its output; ``add_scale`` (float32
+    [N]) multiplies ``add``."""
+    _cuda(h, w_gate_up, w_down, ids, weights, add, act, y, out, work, gathered, add_scale)
+    assert add_scale is None or (add_scale.dtype == torch.float32 and add_scale.numel() == h.shape[0])
     assert gathered is None or (gathered.dtype == torch.bfloat16 and gathered.shape == (h.shape[0] * ids.shape[1], h.shape[1]))
     n, width = h.shape
     e, two_ff, w2 = w_gate_up.shape
@@ -1346,5 +1377,97 @@ def moe_grouped(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     assert work.dtype == torch.int32 and work.numel() >= moe_grouped_workspace(n, top, e)
     limit, alpha, shift = gating if gating is not None else (0.0, 1.0, 0.0)
     check(fn("pb_moe_grouped")(_p(h), _p(w_gate_up), _p(w_down), _p(ids), _p(weights), _p(add), _p(act), _p(y), _p(out), _p(work),
-                               _p(gathered), n, width, ff, e, top, float(limit), float(alpha), float(shift), stream()), "moe_grouped",
+                               _p(gathered), n, width, ff, e, top, float(limit), float(alpha), float(shift), 1 if weight_input else 0,
+                               _p(add_scale), stream()), "moe_grouped",
           kernels=4 if gathered is None else 5)
+
+
+# ---------------------------------------------------------------- parallel sublayers, token shift, recurrences, differential maps
+def norm_shift(ctx, residual: torch.Tensor, weight: torch.Tensor, eps: float, shift: Optional[torch.Tensor],
+               state: Optional[torch.Tensor], h: torch.Tensor, hs: Optional[torch.Tensor], pending: Optional[torch.Tensor]) -> None:
+    """h = rmsnorm(residual) * weight; with ``shift`` [width]: hs = h + (h' - h) * shift, h' the h of the token before in its
+    sequence (the row above, or the sequence's kept row of ``state`` [slots, width] float32 for a portion's first token); the
+    float32 h of every sequence's last token goes to ``pending`` [S, width] (``parallel_add`` moves it into ``state``)."""
+    _cuda(residual, weight, shift, h, hs, pending)
+    n, width = residual.shape
+    assert residual.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == width and h.shape == (n, width)
+    if shift is not None:
+        assert shift.dtype == torch.float32 and shift.numel() == width and hs.shape == (n, width) and hs.dtype == h.dtype
+        assert state.dtype == torch.float32 and state.dim() == 2 and state.shape[1] >= width and state.stride(1) == 1 and state.is_cuda
+        assert pending.dtype == torch.float32 and pending.numel() >= ctx.n_seqs * width
+    check(fn("pb_norm_shift")(code(h.dtype), _p(residual), _p(weight), float(eps), _p(shift), _p(state),
+                              0 if state is None else state.stride(0), _p(ctx.seq_of_token), _p(ctx.cu_q), _p(ctx.state_slots), _p(h),
+                              _p(hs), _p(pending), n, width, stream()), "norm_shift")
+
+
+def parallel_add(ctx, residual: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor], mult: float,
+                 pending: Optional[torch.Tensor] = None, state: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                 next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0, next_shift: Optional[torch.Tensor] = None,
+                 next_state: Optional[torch.Tensor] = None, next_pending: Optional[torch.Tensor] = None,
+                 h: Optional[torch.Tensor] = None, hs: Optional[torch.Tensor] = None) -> None:
+    """residual += mult * (a + b) in float32 (``b`` may be None), and ``pending`` [S, width] -> the kept rows of ``state``.
+    With ``next_weight`` the sum goes to ``out`` (another buffer than ``residual``) and the kernel also does the
+    ``norm_shift`` of the layer that follows on it: ``h``, ``hs``, ``next_pending`` as there."""
+    _cuda(residual, a, b, pending, out, next_weight, next_shift, next_pending, h, hs)
+    n, width = residual.shape
+    assert residual.dtype == torch.float32 and a.shape == (n, width) and (b is None or (b.shape == a.shape and b.dtype == a.dtype))
+    for st in (state, next_state):
+        assert st is None or (st.dtype == torch.float32 and st.dim() == 2 and st.shape[1] >= width and st.stride(1) == 1 and st.is_cuda)
+    assert (pending is None) == (state is None)
+    target = residual if out is None else out
+    assert target.shape == residual.shape and target.dtype == torch.float32
+    if next_weight is not None:
+        assert out is not None and out.data_ptr() != residual.data_ptr() and h is not None and h.dtype == a.dtype
+        assert next_weight.dtype == torch.float32 and next_weight.numel() == width
+        assert next_shift is None or (next_shift.dtype == torch.float32 and hs is not None and next_state is not None
+                                      and next_pending is not None)
+    check(fn("pb_parallel_add")(code(a.dtype), _p(residual), _p(a), _p(b), float(mult), _p(target), _p(pending), _p(state),
+                                0 if state is None else state.stride(0), _p(ctx.seq_of_token), _p(ctx.cu_q), _p(ctx.state_slots),
+                                _p(next_weight), float(next_eps), _p(next_shift), _p(next_state),
+                                0 if next_state is None else next_state.stride(0), _p(next_pending), _p(h), _p(hs), n, width,
+                                stream()), "parallel_add")
+
+
+ACTIVATIONS = {"gelu": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> None:
+    """out = act(x) element by element in float32, one rounding on store; ``kind``: "gelu" (the erf form), "gelu_tanh",
+    "silu", "relu".  ``x`` float32 or of ``out``'s dtype."""
+    _cuda(x, out)
+    assert x.shape == out.shape and kind in ACTIVATIONS
+    check(fn("pb_activation")(code(x.dtype), code(out.dtype), _p(x), _p(out), x.numel(), ACTIVATIONS[kind], stream()), "activation")
+
+
+MIN_GRU_CHUNKED_MIN = 64      # portions of at least this many tokens take the recurrence in runs, parallel over tokens
+
+
+def min_gru(ctx, proj: torch.Tensor, bias_z: torch.Tensor, bias_x: torch.Tensor, state: torch.Tensor, y: torch.Tensor) -> None:
+    """The minimal gated recurrence over the step's tokens: ``proj`` float32 [N, 3 W] holds z | u | g pre-activations,
+    ``state`` [slots, >= W] float32 each sequence's kept state (its first W elements), ``y`` [N, W] = S_t * silu(g_t)."""
+    _cuda(proj, bias_z, bias_x, y)
+    n, w3 = proj.shape
+    width = w3 // 3
+    assert proj.dtype == torch.float32 and w3 == 3 * width and y.shape == (n, width)
+    assert bias_z.dtype == bias_x.dtype == torch.float32 and bias_z.numel() == bias_x.numel() == width
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.shape[1] >= width and state.stride(1) == 1 and state.is_cuda
+    max_runs, run_a, run_b, kernels = 0, None, None, 1
+    if ctx.max_q_len >= MIN_GRU_CHUNKED_MIN:
+        run = fn("pb_min_gru_run")()
+        max_runs = sum(-(-int(q) // run) for q in ctx.host.q_lens)
+        run_a = ctx.scratch("gru.run_a", (max_runs, width), torch.float32)
+        run_b = ctx.scratch("gru.run_b", (max_runs, width), torch.float32)
+        kernels = 3
+    check(fn("pb_min_gru")(code(y.dtype), _p(proj), _p(bias_z), _p(bias_x), _p(state), state.stride(0), _p(ctx.cu_q),
+                           _p(ctx.state_slots), _p(y), n, ctx.n_seqs, width, max_runs, _p(run_a), _p(run_b), stream()), "min_gru",
+          kernels=kernels)
+
+
+def diff_combine(maps: torch.Tensor, out: torch.Tensor, n_kv_heads: int, lam: float, eps: float, gain: float) -> None:
+    """out [N, H, Dv] = unit_rms(a1 - lam * a2) * gain per head, from ``maps`` [N, 2 H, Dv] ordered so that the query heads of
+    one key head are neighbours (head g R + r: first map at row 2 g R + r, second at (2 g + 1) R + r, R = H / n_kv_heads)."""
+    _cuda(maps, out)
+    n, h2, dv = maps.shape
+    assert h2 % 2 == 0 and out.shape == (n, h2 // 2, dv) and (h2 // 2) % n_kv_heads == 0
+    check(fn("pb_diff_combine")(code(maps.dtype), code(out.dtype), _p(maps), _p(out), n, h2 // 2, int(n_kv_heads), dv, float(lam),
+                                float(eps), float(gain), stream()), "diff_combine")

@@ -37,6 +37,14 @@ class Attention(Mixer):
     With any of these the fused projection (rows q | k | v | gate) is a float32 product, the bias is added in float32,
     and ``ops.qk_prepare`` does what stands between it and the attention kernels.
 
+    The differential form (``spec.differential`` = d, part of the general form without rotation, biases or per-head norm):
+    every head has two score maps over the same values.  Its query rows hold [map 1 | map 2] (``head_dim`` each) and so do
+    the key rows of a key/value head; the engine treats the maps as 2 H query heads over 2 G key heads that read G value
+    heads (``v_share`` 2), with the query rows re-ordered once at load so that the query heads of one key head are
+    neighbours, and ``ops.diff_combine`` gives unit_rms(a1 - lambda a2) * (1 - d) per head, lambda = exp(<lq1, lk1>) -
+    exp(<lq2, lk2>) + d.  ``spec.q_temperature`` = (coef, every) multiplies the query at position p by
+    1 + coef * ln(floor((p + 1) / every) + 1) (float32, as the queries are split off the projection row).
+
     ``output_bias`` is the output projection's bias (or None).  ``forward`` adds it unless the block has set
     ``defer_output_bias`` because the kernel behind the mixer takes it along.
     """
@@ -51,8 +59,14 @@ class Attention(Mixer):
         # q | k, so the gate's columns ride along in the same product)
         self.prepared = bool(spec.bias or spec.values_from_keys or not spec.qk_norm_weight or spec.qk_norm_after_rotation
                              or spec.output_gate)
+        self.maps = 2 if spec.differential is not None else 1          # score maps per head
         self.general = bool(spec.value_dim != spec.head_dim or spec.chunk is not None or spec.distance_bias is not None
-                            or spec.keep_first or spec.softcap is not None or spec.sinks or spec.output_gate or self.prepared)
+                            or spec.keep_first or spec.softcap is not None or spec.sinks or spec.output_gate or self.prepared
+                            or self.maps > 1 or spec.q_temperature is not None)
+        if (self.maps > 1 or spec.q_temperature is not None) and (self.prepared or not spec.own_kv):
+            raise ValueError("attention: the differential form and the query temperature go with plain projections of its own keys")
+        if spec.q_temperature is not None and not (int(spec.q_temperature[1]) > 0):
+            raise ValueError("attention: the query temperature's period must be positive")
         if self.general:
             if not self.prepared and (spec.position is not None or spec.qk_norm_eps is not None):
                 raise ValueError("attention: the general form (value width, chunk mask, distance bias) has neither rotation nor q/k norm")
@@ -79,7 +93,9 @@ class Attention(Mixer):
         self.names = {"q": name("q", "q_proj.weight"), "k": name("k", "k_proj.weight"), "v": name("v", "v_proj.weight"),
                       "o": name("o", "o_proj.weight"), "q_norm": name("q_norm", "q_norm.weight"),
                       "k_norm": name("k_norm", "k_norm.weight"), "gate": name("gate", "g_proj.weight"),
-                      "sinks": name("sinks", "sinks")}
+                      "sinks": name("sinks", "sinks"), "lq1": name("lq1", "lambda_q1"), "lk1": name("lk1", "lambda_k1"),
+                      "lq2": name("lq2", "lambda_q2"), "lk2": name("lk2", "lambda_k2")}
+        self.diff_lambda = 0.0
         for role in ("q", "k", "o"):          # a bias is named after its weight unless the specification names it
             weight = self.names[role]
             default = weight[:-len(".weight")] + ".bias" if weight.endswith(".weight") else weight + ".b"
@@ -89,9 +105,9 @@ class Attention(Mixer):
     # ---------------------------------------------------------------- weights
     def weight_specs(self) -> List[WeightSpec]:
         s, p, nm = self.spec, self.prefix, self.names
-        specs = [WeightSpec(p + nm["q"], (s.n_heads * s.head_dim, s.hidden))]
+        specs = [WeightSpec(p + nm["q"], (s.n_heads * self.maps * s.head_dim, s.hidden))]
         if s.own_kv:
-            specs.append(WeightSpec(p + nm["k"], (s.n_kv_heads * s.head_dim, s.hidden)))
+            specs.append(WeightSpec(p + nm["k"], (s.n_kv_heads * self.maps * s.head_dim, s.hidden)))
         if self.own_v:
             specs.append(WeightSpec(p + nm["v"], (s.n_kv_heads * s.value_dim, s.hidden)))
         if s.output_gate:
@@ -104,6 +120,8 @@ class Attention(Mixer):
             specs.append(WeightSpec(p + nm["o_bias"], (s.hidden,), role="vector", init="small"))
         if s.sinks:
             specs.append(WeightSpec(p + nm["sinks"], (s.n_heads,), role="vector", init="small"))
+        if self.maps > 1:
+            specs += [WeightSpec(p + nm[r], (s.head_dim,), role="vector", init="small") for r in ("lq1", "lk1", "lq2", "lk2")]
         if s.qk_norm_eps is not None and s.qk_norm_weight:
             specs.append(WeightSpec(p + nm["q_norm"], (s.head_dim,), role="vector", init="ones_normal"))
             if s.own_kv:
@@ -113,6 +131,15 @@ class Attention(Mixer):
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         s, p, nm = self.spec, self.prefix, self.names
         parts = [tensors[p + nm["q"]]]
+        if self.maps > 1:
+            # stored head by head as [map 1 | map 2]; the kernels want the query heads of one key head side by side:
+            # for key/value head g, map m, head-in-group r:  row block (2 g + m) R + r  <-  stored block 2 (g R + r) + m
+            R, D = s.n_heads // s.n_kv_heads, s.head_dim
+            blocks = parts[0].view(s.n_kv_heads, R, 2, D, s.hidden)
+            parts[0] = blocks.permute(0, 2, 1, 3, 4).reshape(2 * s.n_heads * D, s.hidden).contiguous()
+            # one number for the layer, from the float32 vectors
+            l1, l2 = (torch.exp((tensors[p + nm[a]].double() * tensors[p + nm[b]].double()).sum()) for a, b in (("lq1", "lk1"), ("lq2", "lk2")))
+            self.diff_lambda = float((l1 - l2).item() + float(s.differential))
         if s.own_kv:
             parts.append(tensors[p + nm["k"]])
         if self.own_v:
@@ -140,8 +167,8 @@ class Attention(Mixer):
     def cache_need(self) -> CacheNeed:
         s = self.spec
         # Pages behind a window go back to the pool as the queries pass them, except those of the kept first keys.
-        if s.value_dim != s.head_dim:
-            return CacheNeed.paged((CachedTensor("k", s.n_kv_heads, s.head_dim), CachedTensor("v", s.n_kv_heads, s.value_dim)),
+        if s.value_dim != s.head_dim or self.maps > 1:
+            return CacheNeed.paged((CachedTensor("k", s.n_kv_heads * self.maps, s.head_dim), CachedTensor("v", s.n_kv_heads, s.value_dim)),
                                    s.window, s.keep_first)
         return CacheNeed.paged_kv(s.n_kv_heads, s.head_dim, s.window, s.keep_first)
 
@@ -170,7 +197,8 @@ class Attention(Mixer):
         s = self.spec
         n = ctx.n_tokens
         n_kv = s.n_kv_heads if s.own_kv else 0
-        q = ctx.scratch("attn.q32", (n, s.n_heads, s.head_dim), torch.float32)
+        maps = self.maps
+        q = ctx.scratch("attn.q32", (n, s.n_heads * maps, s.head_dim), torch.float32)
         if self.prepared:
             cos = sin = None
             rotary = 0
@@ -182,10 +210,14 @@ class Attention(Mixer):
                            s.qk_norm_eps, s.values_from_keys)
         else:
             ops.qkv_split_write(qkv, q, cache.k_pool if n_kv else None, cache.v_pool if n_kv else None,
-                                cache.slots if n_kv else None, s.n_heads, n_kv, s.head_dim, s.value_dim, cache.page_size)
-        o = ctx.scratch("attn.o", (n, s.n_heads, s.value_dim))
+                                cache.slots if n_kv else None, s.n_heads * maps, n_kv * maps, s.head_dim, s.value_dim, cache.page_size,
+                                n_value_heads=n_kv, positions=ctx.positions, q_temperature=s.q_temperature)
+        o = ctx.scratch("attn.o", (n, s.n_heads * maps, s.value_dim))
         ops.paged_attention_general(ctx, q, cache.k_pool, cache.v_pool, o, cache.block_table, s.scale, s.window, s.chunk,
-                                    self.slopes, keep_first=s.keep_first, softcap=s.softcap, sinks=self.sinks)
+                                    self.slopes, keep_first=s.keep_first, softcap=s.softcap, sinks=self.sinks, v_share=maps)
+        if maps > 1:
+            both, o = o, ctx.scratch("attn.o.diff", (n, s.n_heads, s.value_dim))
+            ops.diff_combine(both, o, s.n_kv_heads, self.diff_lambda, s.norm_eps, 1.0 - float(s.differential))
         return o
 
     def forward_normed(self, ctx: StepContext, residual: torch.Tensor, norm, cache: CacheView, next_norm=None) -> bool:

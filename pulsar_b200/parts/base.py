@@ -41,6 +41,7 @@ class CacheView:
     page_size: int = 0
     state: Optional[torch.Tensor] = None         # [max_requests, *state_shape]
     group: int = -1
+    block_state: Optional[torch.Tensor] = None   # [max_requests, *shape]: the state the block itself keeps (``Block.state_need``)
 
     @property
     def k_pool(self) -> Optional[torch.Tensor]:
@@ -88,10 +89,15 @@ class StepContext:
         self.prepared_norms: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
         self.next_norm = None                   # the first norm of the block that runs after the current one, if known
         self.has_following = True               # False while the last entry of the run order runs
+        self.next_block = self.next_call = None  # the block that runs after the current one and its entry of the run order, if any
         # A norm that was already applied to the residual as it stands, by that norm's id: the normalised rows in the
         # activation dtype.  Valid while nothing else touches the residual.
         self.normed: Dict[int, torch.Tensor] = {}
         self.on_layer = None                    # called as on_layer(index in the run order, residual, pending delta) behind every layer call
+        # A block may hand the stream on in another buffer than the one it was given (its closing kernel wrote the sum
+        # there because rows of the old one were still being read): it leaves the new buffer here, and whoever drives
+        # the blocks takes it as the residual from then on.
+        self.moved_residual: Optional[torch.Tensor] = None
 
     def scratch(self, tag: str, shape: Sequence[int], dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         return self.runner.scratch(tag, tuple(shape), dtype or self.dtype)
@@ -178,6 +184,12 @@ class Block(Part):
     @property
     def graph_safe(self) -> bool:
         return all(getattr(p, "graph_safe", True) for p in self.parts)
+
+    def state_need(self) -> Optional[CacheNeed]:
+        """What the arrangement itself carries from token to token for every sequence (``CacheNeed.state``), or None.  The
+        run order gives such a block a cache entry of its own (``LayerCall.state``); it reaches ``forward`` as
+        ``cache.block_state``."""
+        return None
 
     def forward(self, ctx: StepContext, residual: torch.Tensor, delta: Optional[torch.Tensor],
                 cache: CacheView) -> torch.Tensor:

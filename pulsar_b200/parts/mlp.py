@@ -133,3 +133,38 @@ class ClampedGLU(FeedForward):
         out = ctx.scratch("mlp.out", (n, s.hidden))
         ops.linear(act, self.w_down, out)
         return out
+
+
+@FEED_FORWARDS.register("mlp")
+class ActivatedMLP(FeedForward):
+    """act(h Wu^T) Wd^T without gate and without bias; ``spec.activation``: "gelu" (the erf form), "gelu_tanh", "silu" or
+    "relu".  The up product leaves float32 rows, the activation runs in float32 and rounds once (``ops.activation``).
+    Options (``spec.extra``): tensor names by role "up", "down"."""
+
+    def __init__(self, spec: FeedForwardSpec, prefix: str, dtype: torch.dtype):
+        if spec.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"mlp: activation '{spec.activation}' is not one of {sorted(ops.ACTIVATIONS)}")
+        self.spec, self.prefix, self.dtype = spec, prefix, dtype
+        names = dict(spec.option("tensor_names", ()))
+        self.names = {r: names.get(r, d) for r, d in (("up", "up_proj.weight"), ("down", "down_proj.weight"))}
+        self.w_up = self.w_down = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        s, p, nm = self.spec, self.prefix, self.names
+        return [WeightSpec(p + nm["up"], (s.intermediate, s.hidden)), WeightSpec(p + nm["down"], (s.hidden, s.intermediate))]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.w_up, self.w_down = tensors[self.prefix + self.names["up"]], tensors[self.prefix + self.names["down"]]
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_up, self.w_down))
+
+    def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
+        s, n = self.spec, ctx.n_tokens
+        up = ctx.scratch("mlp.up32", (n, s.intermediate), torch.float32)
+        ops.linear(h, self.w_up, up)
+        act = ctx.scratch("mlp.act", (n, s.intermediate))
+        ops.activation(up, act, s.activation)
+        out = ctx.scratch("mlp.out", (n, s.hidden))
+        ops.linear(act, self.w_down, out)
+        return out

@@ -20,9 +20,14 @@ class MixtureOfExperts(FeedForward):
     ``spec.intermediate`` is an expert's inner width.  A shared expert (a feed-forward specification of its own under
     the option ``shared``) runs for every token and is added.
 
+    With ``weight_input`` the weight multiplies the expert's input instead of its output, sum of expert_e(w_e h): the gate
+    and up sums are scaled by w_e in float32 before the gating (W (w h) = w (W h)), and the sum over a token's experts
+    takes each once.  With ``shared_gate`` (a tensor name behind the prefix, [1, width]) the shared expert's output is
+    multiplied by sigmoid(<that row, h>), one number per token; the row rides in the router's product as one more row.
+
     Options (``spec.extra``): ``experts``, ``top``, ``router_scale``, ``renormalize``, ``limit``, ``alpha``, ``shift``,
-    ``shared`` (FeedForwardSpec or None), ``shared_prefix`` ("shared."), ``tensor_names`` by role "router", "gate", "up",
-    "down" (an expert's tensors are ``<prefix>e<i>.<name>``).
+    ``weight_input``, ``shared`` (FeedForwardSpec or None), ``shared_prefix`` ("shared."), ``shared_gate``, ``tensor_names``
+    by role "router", "gate", "up", "down" (an expert's tensors are ``<prefix>e<i>.<name>``).
 
     The router's choice stays on the device: the kernels take the chosen ids as an array, so a step of single tokens can
     be captured into a CUDA graph.  Steps of up to ``ops.MOE_GROUPED_MIN`` tokens (and the float32 engine) read each chosen
@@ -41,10 +46,13 @@ class MixtureOfExperts(FeedForward):
         self.gating = (float(limit) if limit else 0.0, float(spec.option("alpha", 1.702)), float(spec.option("shift", 1.0)))
         names = dict(spec.option("tensor_names", ()))
         self.names = {r: names.get(r, d) for r, d in (("router", "router"), ("gate", "gate"), ("up", "up"), ("down", "down"))}
+        self.weight_input = bool(spec.option("weight_input", False))
         shared = spec.option("shared", None)
-        self.shared = None
+        self.shared = self.shared_gate_name = None
         if shared is not None:
             self.shared = FEED_FORWARDS.get(shared.kind)(shared, prefix + str(spec.option("shared_prefix", "shared.")), dtype)
+            if spec.option("shared_gate", None):
+                self.shared_gate_name = prefix + str(spec.option("shared_gate"))
         self.router = self.w_gate_up = self.w_down = None
 
     def _expert(self, i: int, role: str) -> str:
@@ -60,6 +68,8 @@ class MixtureOfExperts(FeedForward):
         specs.append(WeightSpec(self.prefix + self.names["router"], (self.n_experts, s.hidden), role="vector", init="normal"))
         if self.shared is not None:
             specs += self.shared.weight_specs()
+        if self.shared_gate_name is not None:
+            specs.append(WeightSpec(self.shared_gate_name, (1, s.hidden), role="vector", init="normal"))
         return specs
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -68,6 +78,8 @@ class MixtureOfExperts(FeedForward):
                                       for i in range(n)]).contiguous()                      # [E, 2 ff, width]
         self.w_down = torch.stack([tensors[self._expert(i, "down")] for i in range(n)]).contiguous()    # [E, width, ff]
         self.router = tensors[self.prefix + self.names["router"]].contiguous()
+        if self.shared_gate_name is not None:           # one more row of the router's product: it competes for nothing
+            self.router = torch.cat([self.router, tensors[self.shared_gate_name].reshape(1, -1)], dim=0).contiguous()
         if self.shared is not None:
             self.shared.load(tensors)
 
@@ -81,7 +93,8 @@ class MixtureOfExperts(FeedForward):
         s, n, top = self.spec, ctx.n_tokens, self.top
         ids = ctx.scratch("moe.ids", (n, top), torch.int32)
         weights = ctx.scratch("moe.weights", (n, top), torch.float32)
-        ops.moe_route(h, self.router, ids, weights, self.router_scale, self.renormalize)
+        shared_scale = ctx.scratch("moe.shared_scale", (n, 1), torch.float32) if self.shared_gate_name is not None else None
+        ops.moe_route(h, self.router, ids, weights, self.router_scale, self.renormalize, shared_scale)
         shared = self.shared.forward(ctx, h) if self.shared is not None else None
         act = ctx.scratch("moe.act", (n * top, s.intermediate))
         out = ctx.scratch("moe.out", (n, s.hidden))
@@ -89,8 +102,9 @@ class MixtureOfExperts(FeedForward):
             y = ctx.scratch("moe.y", (n * top, s.hidden), torch.float32)
             work = ctx.scratch("moe.work", (ops.moe_grouped_workspace(n, top, self.n_experts),), torch.int32)
             gathered = ctx.scratch("moe.gathered", (n * top, s.hidden)) if ops.MOE_TCGEN05 else None
-            ops.moe_grouped(h, self.w_gate_up, self.w_down, ids, weights, shared, act, y, out, work, self.gating, gathered)
+            ops.moe_grouped(h, self.w_gate_up, self.w_down, ids, weights, shared, act, y, out, work, self.gating, gathered,
+                            weight_input=self.weight_input, add_scale=shared_scale)
             return out
-        ops.moe_gate_up(h, self.w_gate_up, ids, act, self.gating)
-        ops.moe_down(act, self.w_down, ids, weights, shared, out)
+        ops.moe_gate_up(h, self.w_gate_up, ids, act, self.gating, weights if self.weight_input else None)
+        ops.moe_down(act, self.w_down, ids, None if self.weight_input else weights, shared, out, shared_scale)
         return out

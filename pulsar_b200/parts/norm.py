@@ -14,17 +14,21 @@ from .base import Norm, StepContext, WeightSpec
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
     """y = x * rsqrt(mean(x^2) + eps) * w in float32, one rounding on store
-    (pulsar-core/src/kernels/rmsnorm.cu:29-49).  The weight is held in float32."""
+    (pulsar-core/src/kernels/rmsnorm.cu:29-49).  The weight is held in float32.  With ``spec.scalar`` the stored weight
+    is a single number; it is spread over the coordinates once, at load, and the kernels see a vector."""
 
     def __init__(self, spec: NormSpec, prefix: str, dtype: torch.dtype, tag: str = "norm"):
         self.spec, self.prefix, self.dtype, self.tag = spec, prefix, dtype, tag
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> List[WeightSpec]:
-        return [WeightSpec(self.prefix + self.spec.suffix, (self.spec.size,), role="vector", init="ones_normal")]
+        shape = () if self.spec.scalar else (self.spec.size,)
+        return [WeightSpec(self.prefix + self.spec.suffix, shape, role="vector", init="ones_normal")]
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors[self.prefix + self.spec.suffix]
+        if self.spec.scalar:
+            self.weight = self.weight.reshape(1).expand(self.spec.size).contiguous()
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()

@@ -34,6 +34,8 @@ def _draw(spec: WeightSpec, std: float, gen: torch.Generator, device) -> torch.T
         return 0.5 * noise
     if spec.init == "small":
         return 0.1 * noise
+    if spec.init == "unit":                     # blend factors between 0 and 1
+        return torch.rand(spec.shape, generator=gen, dtype=torch.float32, device=device)
     if spec.init == "step_bias":                # softplus of it is a step size around 0.1 to 0.7
         return -1.0 + 0.7 * noise
     if spec.init == "decay_log":                # exp of it is a decay rate between 0.5 and 8
