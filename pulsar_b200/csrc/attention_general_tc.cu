@@ -272,7 +272,8 @@ general_tc_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pool, 
         if (sinks != nullptr && m_run[r] != -INFINITY) l_run[r] += ex2(fmaf(sinks[head], kLog2e, -m_run[r]));
     }
     const float inv0 = l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f, inv1 = l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f;
-    unsigned char* w_s = smem + warp * 16 * DK * 2;          // [16 rows][DV] bf16, swizzled; DV <= DK
+    // (every warp has passed the loop's last barrier, so both query tiles are free: 2 * kBM * DK elements for kWarps * 16 * DV)
+    unsigned char* w_s = smem + warp * 16 * (DV > DK ? DV : DK) * 2;     // [16 rows][DV] bf16, swizzled; DV <= 2 DK
 #pragma unroll
     for (int i = 0; i < kNTiles; ++i) {
         const uint32_t lo_off = tile_offset<DV>(g, i) + (2 * t) * 2, hi_off = tile_offset<DV>(g + 8, i) + (2 * t) * 2;
@@ -296,7 +297,7 @@ template <int DK, int DV>
 int launch_general_tc(const float* q, const void* k_pool, const void* v_pool, void* out, const int* block_table, const int* cu_q,
                       const int* kv_len, const float* slopes, const float* sinks, int n_q_tiles, const TcShape& sh,
                       cudaStream_t stream) {
-    static_assert(DV <= DK && DK % 16 == 0 && DV % 32 == 0 && DK >= 64 && DV >= 64, "tile shapes");
+    static_assert(DV <= 2 * DK && DK % 16 == 0 && DV % 32 == 0 && DK >= 64 && DV >= 64, "tile shapes");
     constexpr int smem = 2 * kBM * DK * 2 + 2 * kBN * (DK + DV) * 2;
     static bool configured = false;
     if (!configured) {
@@ -318,7 +319,7 @@ PB_EXPORT int pb_attention_general_tc_tile(void) { return kBM; }
 PB_EXPORT int pb_attention_general_tc_supported(int dtype, const void* q, const void* k_pool, const void* v_pool, int Hq, int Hkv,
                                                 int Dk, int Dv, int k_stride, int v_stride) {
     if (dtype != PB_BF16 || Hkv <= 0 || Hq <= 0 || Hq % Hkv || Hq > 65535) return 0;
-    if (!((Dk == 64 && Dv == 64) || (Dk == 128 && Dv == 128) || (Dk == 192 && Dv == 128))) return 0;
+    if (!((Dk == 64 && Dv == 64) || (Dk == 64 && Dv == 128) || (Dk == 128 && Dv == 128) || (Dk == 192 && Dv == 128))) return 0;
     if (k_stride < Dk || v_stride < Dv || k_stride % 8 || v_stride % 8) return 0;       // rows start on 16-byte boundaries
     if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) % 16) return 0;
     return 1;
@@ -336,6 +337,8 @@ PB_EXPORT int pb_paged_attention_general_tc(int dtype, const float* q, const voi
         return PB_ERR_BAD_SIZE;
     if (page_size <= 0 || window < 0 || chunk < 0 || keep_first < 0 || !(softcap >= 0.0f)) return PB_ERR_BAD_SIZE;
     const TcShape sh{n_seqs, Hq, Hkv, k_stride, v_stride, page_size, window, chunk, table_stride, scale, keep_first, softcap, v_share};
+    if (Dk == 64 && Dv == 128)
+        return launch_general_tc<64, 128>(q, k_pool, v_pool, out, block_table, cu_q, kv_len, slopes, sinks, n_q_tiles, sh, stream);
     if (Dk == 64)
         return launch_general_tc<64, 64>(q, k_pool, v_pool, out, block_table, cu_q, kv_len, slopes, sinks, n_q_tiles, sh, stream);
     if (Dk == 128)

@@ -936,7 +936,7 @@ def attention(ctx, q: torch.Tensor, cache, out: torch.Tensor, scale: float, wind
 # plain one (a block per token and head) for every other size.  PULSAR_GENERAL_TILED=0 leaves the tiled one out.
 GENERAL_TILED = os.environ.get("PULSAR_GENERAL_TILED", "1") != "0"
 GENERAL_ROWS = 16
-# Steps with portions of GENERAL_TC_MIN tokens or more, on bfloat16 pages with (key, value) widths (64, 64), (128, 128) or
+# Steps with portions of GENERAL_TC_MIN tokens or more, on bfloat16 pages with (key, value) widths (64, 64), (64, 128), (128, 128) or
 # (192, 128), take the tensor-core kernel, which splits queries and softmax weights into two bfloat16 halves each.
 # PULSAR_GENERAL_TC=0 leaves it out.
 GENERAL_TC = os.environ.get("PULSAR_GENERAL_TC", "1") != "0"

@@ -138,5 +138,5 @@ def write_safetensors(path: str, tensors: Iterable[Tuple[str, torch.Tensor]], me
         f.write(blob)
         for _, t in items:
             c = t.detach().contiguous().cpu()
-            f.write(c.view(torch.uint8).numpy().tobytes() if c.numel() else b"")
+            f.write(c.reshape(-1).view(torch.uint8).numpy().tobytes() if c.numel() else b"")       # (a single number has no dimension to view)
     os.replace(tmp, path)

@@ -99,9 +99,21 @@ def router_choice(h: torch.Tensor, router: torch.Tensor, top: int):
     return order, torch.gather(s, 1, order)
 
 
-def mixture_ff(h: torch.Tensor, w: Dict[str, torch.Tensor], mlp: dict) -> torch.Tensor:
+def choice_margins(h: torch.Tensor, router: torch.Tensor, top: int) -> torch.Tensor:
+    """[L]: distance between the logits of the last chosen and the first rejected expert, relative to the largest logit's
+    magnitude (infinite where every expert is chosen).  A small margin is a close call that rounding may decide otherwise."""
+    z = h @ router.T
+    if top >= z.shape[1]:
+        return torch.full((h.shape[0],), float("inf"), dtype=h.dtype)
+    ordered = torch.sort(z, dim=-1, descending=True).values
+    return (ordered[:, top - 1] - ordered[:, top]) / z.abs().max(dim=-1).values.clamp_min(1e-30)
+
+
+def mixture_ff(h: torch.Tensor, w: Dict[str, torch.Tensor], mlp: dict, margins: Optional[list] = None) -> torch.Tensor:
     """sum over the chosen experts of expert(score * h), plus sigmoid(<sg, h>) * shared(h)."""
     ids, scores = router_choice(h, w["router"], int(mlp["router"]["top"]))
+    if margins is not None:
+        margins.append(choice_margins(h, w["router"], int(mlp["router"]["top"])))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, sc in zip(ids[t].tolist(), scores[t]):
@@ -116,8 +128,9 @@ def sub(weights: Dict[str, torch.Tensor], prefix: str, dtype) -> Dict[str, torch
 
 
 def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float64,
-            streams: Optional[list] = None) -> torch.Tensor:
-    """Logits [L, vocab] of one whole sequence.  ``streams``: a list that receives the residual stream behind every layer."""
+            streams: Optional[list] = None, margins: Optional[list] = None) -> torch.Tensor:
+    """Logits [L, vocab] of one whole sequence.  ``streams``: a list that receives the residual stream behind every layer;
+    ``margins``: a list that receives every routed layer's ``choice_margins``."""
     eps, mult = float(cfg["norm"]["eps"]), float(cfg["residual_mult"])
     x = weights["embed"].to(dtype)[torch.tensor(tokens, dtype=torch.long)]
     for i, layer in enumerate(cfg["layers"]):
@@ -134,7 +147,7 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtyp
         mlp = layer.get("mlp")
         if mlp is not None:
             ffw = sub(weights, p + "mlp.", dtype)
-            delta = delta + (dense_ff(h, ffw) if mlp["kind"] == "dense" else mixture_ff(h, ffw, mlp))
+            delta = delta + (dense_ff(h, ffw) if mlp["kind"] == "dense" else mixture_ff(h, ffw, mlp, margins))
         x = x + mult * delta
         if streams is not None:
             streams.append(x.clone())
