@@ -1,7 +1,8 @@
-"""Throughput of another design beside the closest dense model at equal size (``bench.py --design NAME``).
+"""Throughput of another design beside the closest existing model at equal size (``bench.py --design NAME``).
 
 For each size the design's model and a Qwen3 dense model of the same width, depth, heads, feed-forward size and vocabulary
-are built with random weights (bfloat16) and timed through the step function:
+(for Megusun: a Topunex model, the closest one, with the same width, depth, projection sizes, experts and vocabulary; its
+entry keeps the key "dense") are built with random weights (bfloat16) and timed through the step function:
 
   prefill   one step of 2,048 prompt tokens (tokens a second, ms)
   decode    steps of single tokens of 8 requests whose context ends at 2,048 (tokens a second, ms per step)
@@ -65,6 +66,68 @@ def topunex_config(z: dict) -> dict:
     layers = [dict(type="attention", mixer=dict(mixer), mlp=dict(kind="dense", ff=z["ff"]) if i == 0 else dict(moe))
               for i in range(z["layers"])]
     return dict(architecture="Topunex", vocab=z["vocab"], width=z["width"], norm=dict(eps=1e-6), layers=layers)
+
+
+# Megusun at sizes that resemble layers of real models: of every four layers three have the recurrent mixer and one the
+# differential attention (two score maps of 64 per head over values of 128, so a head's query and key rows are as wide as
+# a head of 128); the feed-forwards alternate between a dense one and 32 experts of which a token uses 4, beside a gated
+# shared expert.  The shape also carries what the model beside it needs (Topunex: a window, kept keys, rotating dimensions).
+MEGUSUN_SIZES = {
+    "2k": dict(width=2048, layers=8, heads=16, kv_heads=4, dim=128, map_dim=64, vdim=128, gru=2048, rot=64, window=1024, keep=4,
+               ff=8192, experts=32, top=4, expert_ff=1024, shared_ff=2048, vocab=32000),
+    "4k": dict(width=4096, layers=8, heads=32, kv_heads=8, dim=128, map_dim=64, vdim=128, gru=4096, rot=64, window=1024, keep=4,
+               ff=12288, experts=32, top=4, expert_ff=2048, shared_ff=4096, vocab=32000),
+}
+
+
+def megusun_layers(z: dict):
+    """(mixer type, feed-forward kind) per layer: recurrent + dense, recurrent + experts, attention + dense, recurrent + experts."""
+    pattern = [("mingru", "dense"), ("mingru", "moe"), ("attention", "dense"), ("mingru", "moe")]
+    return [pattern[i % 4] for i in range(z["layers"])]
+
+
+def megusun_config(z: dict) -> dict:
+    att = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["map_dim"], vdim=z["vdim"], scale=1.0 / math.sqrt(z["map_dim"]), diff=0.6,
+               q_temp=dict(coef=0.5, every=64))
+    moe = dict(kind="moe", expert=dict(ff=z["expert_ff"]), router=dict(experts=z["experts"], top=z["top"]), shared=dict(ff=z["shared_ff"]))
+    layers = [dict(type=mixer, mixer=dict(att) if mixer == "attention" else dict(width=z["gru"]),
+                   mlp=dict(kind="dense", ff=z["ff"]) if ff == "dense" else dict(moe)) for mixer, ff in megusun_layers(z)]
+    return dict(architecture="Megusun", vocab=z["vocab"], width=z["width"], norm=dict(eps=1e-6), residual_mult=0.5, layers=layers)
+
+
+def megusun_work(z: dict, phase: str) -> Dict[str, Tuple[float, float, str]]:
+    """Per kernel class of Megusun: (bytes it must move, flops, what the flops run on) summed over the layers of a step."""
+    n = PROMPT if phase == "prefill" else BATCH
+    seqs = 1 if phase == "prefill" else BATCH
+    start = 0 if phase == "prefill" else CONTEXT - 1
+    kinds = megusun_layers(z)
+    L, w = len(kinds), z["width"]
+    La = sum(1 for m, _ in kinds if m == "attention")
+    Lg, Ld, Lm = L - La, sum(1 for _, f in kinds if f == "dense"), sum(1 for _, f in kinds if f == "moe")
+    H, G, D, V, W = z["heads"], z["kv_heads"], z["map_dim"], z["vdim"], z["gru"]
+    E, top, fe, fs = z["experts"], z["top"], z["expert_ff"], z["shared_ff"]
+    steps = 1 if phase == "prefill" else 4
+    pairs = seqs * _pairs(n // seqs, start)
+    keys_read = seqs * (start + n // seqs)
+    attention = (La * (keys_read * (2 * G * D + G * V) * 2 + n * 2 * H * (D * 4 + V * 2)), La * 2.0 * 2 * H * 2 * (D + V) * pairs)
+    distinct = E * (1.0 - (1.0 - top / E) ** n)
+    work = {
+        "paged_attention_general_tc": (attention[0], attention[1], "bf16 tensor"),
+        "paged_attention_general_tiled": (attention[0], attention[1], "fp32 FMA"),
+        "paged_attention_general": (attention[0], attention[1], "fp32 FMA"),
+        "qkv_split_write": (La * n * (2 * H * D * (2 + 4) + (2 * G * D + G * V) * 4), 0.0, ""),
+        "diff_combine": (La * n * H * V * (2 * 2 + 2), 0.0, ""),
+        "norm_shift": (n * w * (4 + 2 + 2), 0.0, ""),                                  # the first layer's; the others' ride in parallel_add
+        "parallel_add": (n * w * ((L - 1) * (4 + 2 + 2 + 4 + 2 + 2) + (4 + 2 + 2 + 4)), 0.0, ""),
+        "activation": (Ld * n * z["ff"] * (4 + 2), 0.0, ""),
+        "min_gru": (Lg * (n * W * (12 + 2) + seqs * W * 8), Lg * n * W * 20.0, "fp32 FMA"),
+        "moe_route": (Lm * (n * w * 2 + (E + 1) * w * 4), 0.0, ""),
+        "moe_grouped": (Lm * (distinct * 3 * w * fe * 2 + n * w * 4 + n * top * (fe * 4 + w * 8)), Lm * 2.0 * n * top * 3 * w * fe, "bf16 tensor"),
+        "moe_gate_up": (Lm * (n * top * 2 * fe * w * 2 + n * w * 2), Lm * 4.0 * n * top * fe * w, "fp32 FMA"),
+        "moe_down": (Lm * (n * top * fe * w * 2 + n * w * 4), Lm * 2.0 * n * top * fe * w, "fp32 FMA"),
+        "silu_mul": (Lm * n * fs * 6, 0.0, ""),
+    }
+    return {k: (b * steps, f * steps, on) for k, (b, f, on) in work.items()}
 
 
 def dense_config(z: dict) -> dict:
@@ -265,26 +328,29 @@ def rooflines(kernels: Dict[str, List[float]], work: Dict[str, Tuple[float, floa
     return out
 
 
-DESIGNS = {"bubotar": (SIZES, bubotar_config, own_work), "topunex": (TOPUNEX_SIZES, topunex_config, topunex_work)}
+# design -> (sizes, its configuration, its kernels' work, the configuration of the model beside it, that model's kernels' work)
+DESIGNS = {"bubotar": (SIZES, bubotar_config, own_work, dense_config, like_work),
+           "topunex": (TOPUNEX_SIZES, topunex_config, topunex_work, dense_config, like_work),
+           "megusun": (MEGUSUN_SIZES, megusun_config, megusun_work, topunex_config, topunex_work)}
 
 
 def run(args, bench) -> dict:
     """``bench``: the bench module (its timing functions, peaks and clock sampler are used as they are)."""
     import torch
     pk = bench.peaks()
-    table, make_config, design_work = DESIGNS[args.design]
+    table, make_config, design_work, beside_config, beside_work = DESIGNS[args.design]
     sizes = [s for s in (args.sizes.split(",") if args.sizes else table) if s]
     line = {"design": args.design, "dtype": "bf16", "data": "synthetic: random weights, random token ids, random cache contents for decode",
             "prompt_tokens": PROMPT, "decode": {"batch": BATCH, "context": CONTEXT}, "peaks": pk, "sizes": {}}
     for size in sizes:
         z = table[size]
         entry = {"shape": z}
-        for who, raw in (("design", make_config(z)), ("dense", dense_config(z))):
+        for who, raw in (("design", make_config(z)), ("dense", beside_config(z))):       # "dense": the model beside it (Qwen3 dense, or Topunex for Megusun)
             engine = build(raw)
             p_seconds = bench.time_prefill(engine, PROMPT)
             d_seconds, _, _ = bench.time_decode(engine, BATCH, CONTEXT, args.steps, max(3, args.warmup))
             prefill_k, decode_k = profiled(engine, bench)
-            work = design_work if who == "design" else like_work
+            work = design_work if who == "design" else beside_work
             entry[who] = {
                 "model": engine.model.spec.architecture, "weights_gb": round(engine.model.weight_bytes(0) / 1e9, 3),
                 "prefill_tokens_per_s": round(PROMPT / p_seconds, 1), "prefill_ms": round(p_seconds * 1e3, 3),

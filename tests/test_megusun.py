@@ -563,7 +563,7 @@ def test_small_kernels_against_their_formulas(dtype):
     ops.qkv_split_write(row.cuda(), q_out, k_pool, v_pool, slot.cuda(), Hq, Hk, D, V, page, n_value_heads=Hv,
                         positions=torch.tensor(positions, dtype=torch.int32).cuda(), q_temperature=(0.8, 7))
     f = torch.tensor([1 + 0.8 * math.log((p + 1) // 7 + 1) for p in positions], dtype=torch.float64)
-    assert float(f[5]) == 1.0 and float(f[6]) > 1.6 and float(f[12]) == float(f[6]) and float(f[13]) > float(f[12])
+    assert float(f[5]) == 1.0 and float(f[6]) > 1.5 and float(f[12]) == float(f[6]) and float(f[13]) > float(f[12])
     close(q_out, row[:, :Hq * D].double().view(nq, Hq, D) * f[:, None, None], "queries with their temperature", 1e-6)
     for t in range(nq):
         pg, off = int(slot[t]) // page, int(slot[t]) % page
