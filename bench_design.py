@@ -183,10 +183,12 @@ def profiled(engine, bench) -> Tuple[Dict[str, List[float]], Dict[str, List[floa
                     for rid in rids:
                         cache.open(rid)
                         cache.append(rid, CONTEXT - 5)
-                    runner.step([StepEntry(rid, [1], [0]) for rid in rids])
+                    # every request its own random token: requests that all fed the same one would choose the same experts
+                    toks = torch.randint(0, vocab, (5, BATCH), generator=gen).tolist()
+                    runner.step([StepEntry(rid, [toks[4][b]], [0]) for b, rid in enumerate(rids)])
                     profiling.reset()
-                    for _ in range(4):
-                        runner.step([StepEntry(rid, [1], [0]) for rid in rids])
+                    for i in range(4):
+                        runner.step([StepEntry(rid, [toks[i][b]], [0]) for b, rid in enumerate(rids)])
                     if measured:
                         out.append(profiling.totals()[0])
                     for rid in rids:

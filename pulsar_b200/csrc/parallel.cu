@@ -10,11 +10,17 @@
 //   parallel_add   x += m * (a + b) in float32 on the float32 stream (b optional), and the move of `pending` into the kept
 //                  rows.  With `next`: also the norm_shift of the layer that follows, on the stream as it then stands; the
 //                  new stream goes to `x_out`, another buffer than `x`, because a row's blend reads the row above as it was.
+//                  Both kernels have a form that moves four elements at a time and keeps a token's row (and the row above)
+//                  in registers between the sum of squares and the output; it takes widths that are multiples of four up
+//                  to 8192 with 16-byte aligned rows, the plain form everything else.  A layer's two ends always take the
+//                  same form, so the fused boundary and the two separate kernels give the same bits.
 //   activation     out = act(in) element by element, in [N, F] float32 or the activation dtype: 0 gelu (erf), 1 gelu (tanh
 //                  form), 2 silu, 3 relu.  float32 arithmetic, one rounding on store.
 #include "common.cuh"
 
 #include <stdint.h>
+
+#include <initializer_list>
 
 namespace {
 
@@ -61,10 +67,73 @@ __device__ __forceinline__ void norm_shift_row(const Row& row, int t, const Shif
     }
 }
 
+// ---- four elements at a time
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    return make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const unsigned*>(&lo);
+    raw.y = *reinterpret_cast<const unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+__device__ __forceinline__ float dot4(float4 v) { return v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+
+constexpr int kVecIters = 4;            // a thread holds up to 4 x 4 elements of a row: widths up to 4 * 512 * 4
+
+// norm_shift_row with the row in registers.  `cur` holds the thread's part of row t on entry (the caller loaded it, and may
+// have stored it as the new stream); the row above is loaded here through `row.at4`.
+template <typename T, typename Row>
+__device__ __forceinline__ void norm_shift_row4(const Row& row, int t, const float4 (&cur)[kVecIters], const ShiftArgs& p,
+                                                T* __restrict__ h_out, T* __restrict__ hs_out, int width, float* scratch) {
+    const int s = p.seq_of_token[t];
+    const int first = p.cu_q[s], last = p.cu_q[s + 1] - 1;
+    const bool has_prev = p.shift != nullptr && t > first;
+    const int quads = width >> 2;
+    float4 prev[kVecIters];
+    float ss = 0.0f, ssp = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kVecIters; ++k) {
+        const int q = threadIdx.x + k * blockDim.x;
+        if (q < quads) {
+            ss += dot4(cur[k]);
+            if (has_prev) { prev[k] = row.at4(t - 1, q); ssp += dot4(prev[k]); }
+        }
+    }
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)width + p.eps);
+    const float invp = has_prev ? rsqrtf(block_sum(ssp, scratch) / (float)width + p.eps) : 0.0f;
+    const float* kept = p.state + (size_t)p.state_slots[s] * p.state_stride;
+#pragma unroll
+    for (int k = 0; k < kVecIters; ++k) {
+        const int q = threadIdx.x + k * blockDim.x;
+        if (q < quads) {
+            const size_t at = (size_t)t * width + 4 * q;
+            const float4 w = load4(p.weight + 4 * q);
+            const float4 h = make_float4(cur[k].x * inv * w.x, cur[k].y * inv * w.y, cur[k].z * inv * w.z, cur[k].w * inv * w.w);
+            store4(h_out + at, h);
+            if (p.shift != nullptr) {
+                float4 hp;
+                if (has_prev) hp = make_float4(prev[k].x * invp * w.x, prev[k].y * invp * w.y, prev[k].z * invp * w.z, prev[k].w * invp * w.w);
+                else hp = load4(kept + 4 * q);
+                const float4 m = load4(p.shift + 4 * q);
+                store4(hs_out + at, make_float4(h.x + (hp.x - h.x) * m.x, h.y + (hp.y - h.y) * m.y, h.z + (hp.z - h.z) * m.z,
+                                                h.w + (hp.w - h.w) * m.w));
+                if (t == last) store4(p.pending + (size_t)s * width + 4 * q, h);
+            }
+        }
+    }
+}
+
 struct PlainRow {
     const float* x;
     int width;
     __device__ __forceinline__ float operator()(int t, int i) const { return x[(size_t)t * width + i]; }
+    __device__ __forceinline__ float4 at4(int t, int q) const { return load4(x + (size_t)t * width + 4 * q); }
 };
 
 template <typename T>
@@ -73,6 +142,21 @@ __global__ void norm_shift_kernel(const float* __restrict__ x, const ShiftArgs p
     pdl_wait();
     __shared__ float scratch[32];
     norm_shift_row<T>(PlainRow{x, width}, blockIdx.x, p, h_out, hs_out, width, scratch);
+}
+
+template <typename T>
+__global__ void norm_shift4_kernel(const float* __restrict__ x, const ShiftArgs p, T* __restrict__ h_out, T* __restrict__ hs_out,
+                                   int width) {
+    pdl_wait();
+    __shared__ float scratch[32];
+    const PlainRow row{x, width};
+    float4 cur[kVecIters];
+#pragma unroll
+    for (int k = 0; k < kVecIters; ++k) {
+        const int q = threadIdx.x + k * blockDim.x;
+        if (q < (width >> 2)) cur[k] = row.at4(blockIdx.x, q);
+    }
+    norm_shift_row4<T>(row, blockIdx.x, cur, p, h_out, hs_out, width, scratch);
 }
 
 template <typename T>
@@ -86,6 +170,13 @@ struct SumRow {
         const size_t at = (size_t)t * width + i;
         const float d = to_float(a[at]) + (b != nullptr ? to_float(b[at]) : 0.0f);
         return x[at] + m * d;
+    }
+    __device__ __forceinline__ float4 at4(int t, int q) const {
+        const size_t at = (size_t)t * width + 4 * q;
+        const float4 xv = load4(x + at), av = load4(a + at);
+        float4 d = av;
+        if (b != nullptr) { const float4 bv = load4(b + at); d = make_float4(av.x + bv.x, av.y + bv.y, av.z + bv.z, av.w + bv.w); }
+        return make_float4(xv.x + m * d.x, xv.y + m * d.y, xv.z + m * d.z, xv.w + m * d.w);
     }
 };
 
@@ -118,6 +209,33 @@ __global__ void parallel_add_kernel(const float* __restrict__ x, const T* __rest
     if (next.weight != nullptr) norm_shift_row<T>(row, t, next, h_out, hs_out, width, scratch);
 }
 
+template <typename T>
+__global__ void parallel_add4_kernel(const float* __restrict__ x, const T* __restrict__ a, const T* __restrict__ b, float m,
+                                     float* __restrict__ x_out, const CommitArgs c, const ShiftArgs next, T* __restrict__ h_out,
+                                     T* __restrict__ hs_out, int width) {
+    pdl_wait();
+    __shared__ float scratch[32];
+    const int t = blockIdx.x, quads = width >> 2;
+    const SumRow<T> row{x, a, b, m, width};
+    float4 cur[kVecIters];
+#pragma unroll
+    for (int k = 0; k < kVecIters; ++k) {
+        const int q = threadIdx.x + k * blockDim.x;
+        if (q < quads) {
+            cur[k] = row.at4(t, q);
+            store4(x_out + (size_t)t * width + 4 * q, cur[k]);
+        }
+    }
+    if (c.pending != nullptr) {
+        const int s = c.seq_of_token[t];
+        if (t == c.cu_q[s + 1] - 1) {
+            float* kept = c.state + (size_t)c.state_slots[s] * c.state_stride;
+            for (int q = threadIdx.x; q < quads; q += blockDim.x) store4(kept + 4 * q, load4(c.pending + (size_t)s * width + 4 * q));
+        }
+    }
+    if (next.weight != nullptr) norm_shift_row4<T>(row, t, cur, next, h_out, hs_out, width, scratch);
+}
+
 __device__ __forceinline__ float act_value(float z, int kind) {
     if (kind == 0) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
     if (kind == 1) return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
@@ -138,6 +256,17 @@ int row_threads(int width) {
     return threads > 512 ? 512 : (threads < 32 ? 32 : threads);
 }
 
+bool aligned16(const void* p) { return p == nullptr || ((uintptr_t)p & 15) == 0; }
+
+// whether the four-at-a-time form takes these rows: `wide` pointers hold float32 rows, `narrow` ones rows of the activation
+// dtype (8-byte steps of four bfloat16 elements need 8-byte alignment; 16 is asked of all)
+bool vector_rows(int width, long stride_a, long stride_b, std::initializer_list<const void*> pointers) {
+    if (width % 4 != 0 || width > 4 * 512 * kVecIters || stride_a % 4 != 0 || stride_b % 4 != 0) return false;
+    for (const void* p : pointers)
+        if (!aligned16(p)) return false;
+    return true;
+}
+
 }  // namespace
 
 // x [n, width] float32; weight [width]; shift [width] or null (then hs, state, pending and the index arrays are unused);
@@ -149,6 +278,14 @@ PB_EXPORT int pb_norm_shift(int dtype, const float* x, const float* weight, floa
     if (width <= 0 || seq_of_token == nullptr || cu_q == nullptr) return PB_ERR_BAD_SIZE;
     if (shift != nullptr && (state == nullptr || state_slots == nullptr || pending == nullptr || hs == nullptr)) return PB_ERR_BAD_SIZE;
     const ShiftArgs p{weight, shift, state, state_stride, seq_of_token, cu_q, state_slots, pending, eps};
+    if (vector_rows(width, state_stride, 0, {x, weight, shift, state, h, hs, pending})) {
+        if (dtype == PB_F32)
+            return launch_pdl(norm_shift4_kernel<float>, dim3(n), dim3(row_threads(width)), 0, stream, x, p, (float*)h, (float*)hs, width);
+        if (dtype == PB_BF16)
+            return launch_pdl(norm_shift4_kernel<__nv_bfloat16>, dim3(n), dim3(row_threads(width)), 0, stream, x, p, (__nv_bfloat16*)h,
+                              (__nv_bfloat16*)hs, width);
+        return PB_ERR_BAD_DTYPE;
+    }
     if (dtype == PB_F32)
         return launch_pdl(norm_shift_kernel<float>, dim3(n), dim3(row_threads(width)), 0, stream, x, p, (float*)h, (float*)hs, width);
     if (dtype == PB_BF16)
@@ -172,6 +309,17 @@ PB_EXPORT int pb_parallel_add(int dtype, const float* x, const void* a, const vo
         return PB_ERR_BAD_SIZE;
     const CommitArgs c{pending, state, state_stride, seq_of_token, cu_q, state_slots};
     const ShiftArgs nx{next_weight, next_shift, next_state, next_state_stride, seq_of_token, cu_q, state_slots, next_pending, next_eps};
+    if (vector_rows(width, state_stride, next_state_stride, {x, a, b, x_out, pending, state, next_weight, next_shift, next_state,
+                                                             next_pending, h, hs})) {
+        if (dtype == PB_F32)
+            return launch_pdl(parallel_add4_kernel<float>, dim3(n), dim3(row_threads(width)), 0, stream, x, (const float*)a,
+                              (const float*)b, m, x_out, c, nx, (float*)h, (float*)hs, width);
+        if (dtype == PB_BF16)
+            return launch_pdl(parallel_add4_kernel<__nv_bfloat16>, dim3(n), dim3(row_threads(width)), 0, stream, x,
+                              (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, m, x_out, c, nx, (__nv_bfloat16*)h, (__nv_bfloat16*)hs,
+                              width);
+        return PB_ERR_BAD_DTYPE;
+    }
     if (dtype == PB_F32)
         return launch_pdl(parallel_add_kernel<float>, dim3(n), dim3(row_threads(width)), 0, stream, x, (const float*)a, (const float*)b, m,
                           x_out, c, nx, (float*)h, (float*)hs, width);
