@@ -17,7 +17,9 @@ namespace {
 
 using namespace pb;
 
-__device__ __forceinline__ float sigmoidf(float v) { return 1.0f / (1.0f + expf(-v)); }
+// the exponential is the library's; the reciprocal is the special-function unit's (two units in the last place, and exactly 0
+// where 1 + e^-v has left its range): the kernels below spend most of their instructions on these
+__device__ __forceinline__ float sigmoidf(float v) { return __fdividef(1.0f, 1.0f + expf(-v)); }
 
 __device__ __forceinline__ void gru_gates(float z, float u, float bz, float bx, float& zz, float& cand) {
     zz = sigmoidf(z + bz);
@@ -58,7 +60,7 @@ __global__ void min_gru_kernel(const float* __restrict__ proj, const float* __re
     *kept = S;
 }
 
-constexpr int kRun = 32;
+constexpr int kRun = 16;
 
 // runs of a step: sequence s has ceil(q_len / kRun) of them; run_seq / run_first list them (built on the device by pass 1's
 // first block would need a scan; the host gives an upper bound and every block finds its run by walking cu_q).
@@ -119,11 +121,21 @@ __global__ void min_gru_carry_kernel(float* __restrict__ run_a, float* __restric
     const int runs = (cu_q[s + 1] - cu_q[s] + kRun - 1) / kRun;
     float* kept = state + (size_t)state_slots[s] * state_stride + c;
     float S = *kept;
-    for (int r = 0; r < runs; ++r) {
-        const size_t at = (size_t)(run0 + r) * W + c;
-        const float A = run_a[at], B = run_b[at];
-        run_b[at] = S;
-        S = A * S + B;
+    constexpr int U = 16;       // the runs' products do not depend on the fold: sixteen runs' loads in flight
+    for (int r = 0; r < runs; r += U) {
+        float A[U], B[U];
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+            const size_t at = (size_t)(run0 + (r + k < runs ? r + k : r)) * W + c;
+            A[k] = run_a[at]; B[k] = run_b[at];
+        }
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+            if (r + k < runs) {
+                run_b[(size_t)(run0 + r + k) * W + c] = S;
+                S = A[k] * S + B[k];
+            }
+        }
     }
     *kept = S;
 }
@@ -184,7 +196,8 @@ PB_EXPORT int pb_min_gru(int dtype, const float* proj, const float* bz, const fl
     const dim3 grid_r((W + threads - 1) / threads, max_runs);
     int rc = launch_pdl(min_gru_runs_kernel, grid_r, block, 0, stream, proj, bz, bx, cu_q, n_seqs, run_a, run_b, W);
     if (rc != 0) return rc;
-    rc = launch_pdl(min_gru_carry_kernel, grid_s, block, 0, stream, run_a, run_b, state, state_stride, cu_q, state_slots, W);
+    // the fold is a chain of a few dependent steps per channel: warps of their own, spread over the SMs
+    rc = launch_pdl(min_gru_carry_kernel, dim3((W + 31) / 32, n_seqs), dim3(32), 0, stream, run_a, run_b, state, state_stride, cu_q, state_slots, W);
     if (rc != 0) return rc;
     if (dtype == PB_F32)
         return launch_pdl(min_gru_outputs_kernel<float>, grid_r, block, 0, stream, proj, bz, bx, cu_q, n_seqs, (const float*)run_b, (float*)y, W);
