@@ -20,7 +20,7 @@
 // not depend on how the tokens were cut into steps, on what else is in the batch or on which
 // pages hold the keys.  Prompt portions and single decoded tokens take the same kernel.
 //
-// Layouts: q [N, Hq, Dk] float32; out [N, Hq, Dv] T; pools [pages, Hkv, page_size, stride] T;
+// Layouts: q [N, Hq, Dk] float32; out [N, Hq, Dv] T (float32 with out_f32); pools [pages, Hkv, page_size, stride] T;
 // block_table [S, table_stride]; cu_q [S+1]; kv_len [S] (after this step); seq_of_token [N].
 //
 // Also here: the kernel that splits a fused projection row [q | k | v] of such widths into float32
@@ -58,7 +58,14 @@ struct GeneralShape {
     int keep_first;     // keys below this stay visible whatever the window or chunk says; 0: none
     float softcap;      // > 0: scaled scores are capped to softcap * tanh(score / softcap)
     int v_share;        // consecutive key heads that read one value head (the value pool has Hkv / v_share heads); 1: a value head per key head
+    int out_f32;        // the output rows are float32 whatever the pools' type (what follows subtracts them from one another)
 };
+
+template <typename T>
+__device__ __forceinline__ void store_out(T* out, size_t at, float v, int out_f32) {
+    if (out_f32) reinterpret_cast<float*>(out)[at] = v;
+    else out[at] = from_float<T>(v);
+}
 
 // Tiles of 32 keys that a query (or a block of queries) with lowest key `lo` walks over: the tiles that hold kept first
 // keys and lie wholly below the tile of `lo`, then the tiles from that of `lo` on.  n_kept is the count of the former.
@@ -170,12 +177,12 @@ paged_attention_general_kernel(const float* __restrict__ q, const T* __restrict_
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) { f[w] = (m_s[w] == -INFINITY) ? 0.0f : expf(m_s[w] - m_all); l_all += l_s[w] * f[w]; }
     if (sinks) l_all += expf(sinks[h] - m_all);
-    T* ov = out + ((size_t)t * sh.Hq + h) * Dv;
+    const size_t ov = ((size_t)t * sh.Hq + h) * Dv;
     for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
         float o = 0.0f;
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) o += acc_s[w * Dv + d] * f[w];
-        ov[d] = from_float<T>(o / l_all);
+        store_out(out, ov + d, o / l_all, sh.out_f32);
     }
 }
 
@@ -415,12 +422,11 @@ general_tiled_kernel(const float* __restrict__ q, const T* __restrict__ k_pool, 
         if (warp * 4 + r >= n_rows) continue;
         const size_t row = (size_t)tok[r] * sh.Hq + head[r];
         if (ts.n_splits == 1) {
-            T* ov = out + row * Dv;
             const float inv = 1.0f / (sinks ? l_run[r] + expf(sinks[head[r]] - m_run[r]) : l_run[r]);
 #pragma unroll
             for (int i = 0; i < ACC; ++i) {
                 const int c = lane + 32 * i;
-                if (c < Dv) ov[c] = from_float<T>(acc[r][i] * inv);
+                if (c < Dv) store_out(out, row * Dv + c, acc[r][i] * inv, sh.out_f32);
             }
         } else {
             float* pp = partial + (row * ts.n_splits + split) * (Dv + 2);
@@ -438,7 +444,7 @@ general_tiled_kernel(const float* __restrict__ q, const T* __restrict__ k_pool, 
 // weighted sum of their sums.  One block per (token, head).
 template <typename T>
 __global__ void general_combine_kernel(const float* __restrict__ partial, T* __restrict__ out, const float* __restrict__ sinks,
-                                       int Hq, int n_splits, int Dv) {
+                                       int Hq, int n_splits, int Dv, int out_f32) {
     const size_t row = blockIdx.x;
     const float* pp = partial + row * n_splits * (Dv + 2);
     float m_all = -INFINITY;
@@ -455,7 +461,7 @@ __global__ void general_combine_kernel(const float* __restrict__ partial, T* __r
             const float m = pp[(size_t)z * (Dv + 2)];
             if (m != -INFINITY) o += pp[(size_t)z * (Dv + 2) + 2 + c] * expf(m - m_all);
         }
-        out[row * Dv + c] = from_float<T>(o / l_all);
+        store_out(out, row * Dv + c, o / l_all, out_f32);
     }
 }
 
@@ -482,7 +488,7 @@ int launch_tiled(const float* q, const void* k_pool, const void* v_pool, void* o
     if (status == 0 && ts.n_splits > 1) {
         int b = 32;
         while (b < ts.g.Dv && b < 256) b <<= 1;
-        general_combine_kernel<T><<<n_tokens * ts.g.Hq, b, 0, stream>>>(partial, (T*)out, sinks, ts.g.Hq, ts.n_splits, ts.g.Dv);
+        general_combine_kernel<T><<<n_tokens * ts.g.Hq, b, 0, stream>>>(partial, (T*)out, sinks, ts.g.Hq, ts.n_splits, ts.g.Dv, ts.g.out_f32);
         status = launch_status();
     }
     return status;
@@ -553,13 +559,14 @@ PB_EXPORT int pb_paged_attention_general(int dtype, const float* q, const void* 
                                          const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
                                          const int* seq_of_token, const float* slopes, int n_tokens, int Hq, int Hkv, int Dk,
                                          int Dv, int k_stride, int v_stride, int page_size, float scale, int window, int chunk,
-                                         int keep_first, float softcap, const float* sinks, int v_share, cudaStream_t stream) {
+                                         int keep_first, float softcap, const float* sinks, int v_share, int out_f32, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (Dk <= 0 || Dv <= 0 || Dk > 4096 || Dv > 1024 || Hkv <= 0 || Hq <= 0 || Hq % Hkv || page_size <= 0 || k_stride < Dk ||
         v_stride < Dv || window < 0 || chunk < 0 || keep_first < 0 || !(softcap >= 0.0f) || v_share <= 0 || Hkv % v_share)
         return PB_ERR_BAD_SIZE;
     if (Hq > 65535) return PB_ERR_TOO_LARGE;
-    GeneralShape sh{Hq, Hkv, Dk, Dv, k_stride, v_stride, page_size, window, chunk, table_stride, 0, scale, keep_first, softcap, v_share};
+    GeneralShape sh{Hq, Hkv, Dk, Dv, k_stride, v_stride, page_size, window, chunk, table_stride, 0, scale, keep_first, softcap, v_share,
+                    out_f32 != 0};
     if (dtype == PB_F32)
         return dispatch_general<float>(q, k_pool, v_pool, out, block_table, cu_q, kv_len, seq_of_token, slopes, sinks, n_tokens, sh,
                                        stream);
@@ -605,7 +612,7 @@ PB_EXPORT int pb_paged_attention_general_tiled(int dtype, const float* q, const 
                                                const int* kv_len, const float* slopes, int n_tokens, int n_seqs, int row_tiles,
                                                int n_splits, int Hq, int Hkv, int Dk, int Dv, int k_stride, int v_stride,
                                                int page_size, float scale, int window, int chunk, int keep_first, float softcap,
-                                               const float* sinks, int v_share, cudaStream_t stream) {
+                                               const float* sinks, int v_share, int out_f32, cudaStream_t stream) {
     if (n_tokens <= 0 || row_tiles <= 0) return 0;
     if (v_share <= 0 || Hkv % v_share) return PB_ERR_BAD_SIZE;
     if (!pb_attention_general_tiled_supported(dtype, k_pool, v_pool, Hq, Hkv, Dk, Dv, k_stride, v_stride)) return PB_ERR_BAD_SIZE;
@@ -614,7 +621,8 @@ PB_EXPORT int pb_paged_attention_general_tiled(int dtype, const float* q, const 
         return PB_ERR_BAD_SIZE;
     if (Hkv > 65535) return PB_ERR_TOO_LARGE;
     TiledShape ts{};
-    ts.g = GeneralShape{Hq, Hkv, Dk, Dv, k_stride, v_stride, page_size, window, chunk, table_stride, 0, scale, keep_first, softcap, v_share};
+    ts.g = GeneralShape{Hq, Hkv, Dk, Dv, k_stride, v_stride, page_size, window, chunk, table_stride, 0, scale, keep_first, softcap, v_share,
+                        out_f32 != 0};
     ts.n_seqs = n_seqs;
     ts.n_splits = n_splits;
     if (dtype == PB_F32) {

@@ -51,6 +51,7 @@ struct TcShape {
     int keep_first;
     float softcap;
     int v_share;        // consecutive key heads that read one value head (the value pool has Hkv / v_share heads)
+    int out_f32;        // the output rows are float32: the accumulators go out as they are, without the round to bfloat16
 };
 
 __device__ __forceinline__ int lowest_key(int pos, const TcShape& sh) {
@@ -272,6 +273,21 @@ general_tc_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pool, 
         if (sinks != nullptr && m_run[r] != -INFINITY) l_run[r] += ex2(fmaf(sinks[head], kLog2e, -m_run[r]));
     }
     const float inv0 = l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f, inv1 = l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f;
+    if (sh.out_f32) {
+        // a lane's accumulators are pairs of neighbours in rows g and g + 8 of the warp's 16: 8 bytes a store, 32 in a row per quad
+        float* out32 = reinterpret_cast<float*>(out);
+        const int m_lo = warp * 16 + g, m_hi = m_lo + 8;
+#pragma unroll
+        for (int i = 0; i < kNTiles; ++i) {
+            if (m_lo < rows)
+                *reinterpret_cast<float2*>(out32 + ((size_t)(q0 + m0 + m_lo) * sh.Hq + head) * DV + 8 * i + 2 * t) =
+                    make_float2(o[i][0] * inv0, o[i][1] * inv0);
+            if (m_hi < rows)
+                *reinterpret_cast<float2*>(out32 + ((size_t)(q0 + m0 + m_hi) * sh.Hq + head) * DV + 8 * i + 2 * t) =
+                    make_float2(o[i][2] * inv1, o[i][3] * inv1);
+        }
+        return;
+    }
     // (every warp has passed the loop's last barrier, so both query tiles are free: 2 * kBM * DK elements for kWarps * 16 * DV)
     unsigned char* w_s = smem + warp * 16 * (DV > DK ? DV : DK) * 2;     // [16 rows][DV] bf16, swizzled; DV <= 2 DK
 #pragma unroll
@@ -325,18 +341,19 @@ PB_EXPORT int pb_attention_general_tc_supported(int dtype, const void* q, const 
     return 1;
 }
 
-// q float32 [N, Hq, Dk]; out bfloat16 [N, Hq, Dv]; pools bfloat16 [pages, Hkv, page_size, stride].
+// q float32 [N, Hq, Dk]; out bfloat16 [N, Hq, Dv] (float32 with out_f32); pools bfloat16 [pages, Hkv, page_size, stride].
 PB_EXPORT int pb_paged_attention_general_tc(int dtype, const float* q, const void* k_pool, const void* v_pool, void* out,
                                             const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
                                             const float* slopes, int n_seqs, int n_q_tiles, int Hq, int Hkv, int Dk, int Dv,
                                             int k_stride, int v_stride, int page_size, float scale, int window, int chunk,
-                                            int keep_first, float softcap, const float* sinks, int v_share, cudaStream_t stream) {
+                                            int keep_first, float softcap, const float* sinks, int v_share, int out_f32, cudaStream_t stream) {
     if (n_seqs <= 0 || n_q_tiles <= 0) return 0;
     if (v_share <= 0 || Hkv % v_share) return PB_ERR_BAD_SIZE;
     if (!pb_attention_general_tc_supported(dtype, q, k_pool, v_pool, Hq, Hkv, Dk, Dv, k_stride, v_stride) || ((uintptr_t)out % 16))
         return PB_ERR_BAD_SIZE;
     if (page_size <= 0 || window < 0 || chunk < 0 || keep_first < 0 || !(softcap >= 0.0f)) return PB_ERR_BAD_SIZE;
-    const TcShape sh{n_seqs, Hq, Hkv, k_stride, v_stride, page_size, window, chunk, table_stride, scale, keep_first, softcap, v_share};
+    const TcShape sh{n_seqs, Hq, Hkv, k_stride, v_stride, page_size, window, chunk, table_stride, scale, keep_first, softcap, v_share,
+                     out_f32 != 0};
     if (Dk == 64 && Dv == 128)
         return launch_general_tc<64, 128>(q, k_pool, v_pool, out, block_table, cu_q, kv_len, slopes, sinks, n_q_tiles, sh, stream);
     if (Dk == 64)

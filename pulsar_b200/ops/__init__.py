@@ -84,12 +84,12 @@ _SIGNATURES = {
     "pb_sample": [_P, _I, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P],
     "pb_sample_workspace": [_I],
     "pb_argmax": [_P, _I, _I, _P, _P, _P],
-    "pb_paged_attention_general": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _P],
+    "pb_paged_attention_general": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _I, _P],
     "pb_attention_general_tiled_supported": [_I, _P, _P, _I, _I, _I, _I, _I, _I],
-    "pb_paged_attention_general_tiled": [_I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _P],
+    "pb_paged_attention_general_tiled": [_I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _I, _P],
     "pb_attention_general_tc_tile": [],
     "pb_attention_general_tc_supported": [_I, _P, _P, _P, _I, _I, _I, _I, _I, _I],
-    "pb_paged_attention_general_tc": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _P],
+    "pb_paged_attention_general_tc": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _I, _P],
     "pb_qkv_split_write": [_I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _F, _I, _P],
     "pb_heads_linear": [_I, _I, _P, _L, _I, _P, _P, _L, _I, _P, _L, _I, _I, _I, _I, _P],
     "pb_latent_prepare": [_I, _P, _L, _P, _L, _P, _F, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -971,7 +971,8 @@ def paged_attention_general(ctx, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     ``tiled``: None picks the tiled kernel where it applies, False forces the plain one.  ``tensor_cores``: None picks the
     tensor-core kernel for steps with portions where it applies, False never, True insists.
     ``v_share``: that many consecutive key heads read one value head (``v_pool`` has Hkv / v_share heads): several score
-    maps over the same values."""
+    maps over the same values.  ``out`` has the pools' dtype or float32 (rows that are subtracted from one another afterwards
+    stay unrounded)."""
     _cuda(q, k_pool, v_pool, out, block_table, slopes, sinks)
     _check_against(k_pool)
     n, hq, dk = q.shape
@@ -980,7 +981,9 @@ def paged_attention_general(ctx, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     pages, hkv, page_size, k_stride = k_pool.shape
     v_stride = v_pool.shape[3]
     dv = out.shape[2]
-    assert q.dtype == torch.float32 and k_pool.dtype == v_pool.dtype == out.dtype and out.shape[:2] == (n, hq)
+    assert q.dtype == torch.float32 and k_pool.dtype == v_pool.dtype and out.dtype in (k_pool.dtype, torch.float32)
+    assert out.shape[:2] == (n, hq)
+    pool_code, out_f32 = code(k_pool.dtype), int(out.dtype == torch.float32)
     v_share = int(v_share)
     assert (key_width or k_stride) == dk and (value_width or v_stride) == dv and v_share >= 1 and hkv % v_share == 0
     assert v_pool.shape[:3] == (pages, hkv // v_share, page_size)
@@ -991,38 +994,38 @@ def paged_attention_general(ctx, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     if tensor_cores is None:
         tensor_cores = GENERAL_TC and max(q_lens) >= GENERAL_TC_MIN
     if tensor_cores:
-        fits = fn("pb_attention_general_tc_supported")(code(out.dtype), _p(q), _p(k_pool), _p(v_pool), hq, hkv, dk, dv, k_stride,
+        fits = fn("pb_attention_general_tc_supported")(pool_code, _p(q), _p(k_pool), _p(v_pool), hq, hkv, dk, dv, k_stride,
                                                        v_stride)
         if fits:
             rows = fn("pb_attention_general_tc_tile")()
             n_q_tiles = sum(-(-int(ql) // rows) for ql in q_lens)
-            check(fn("pb_paged_attention_general_tc")(code(out.dtype), _p(q), _p(k_pool), _p(v_pool), _p(out), _p(block_table),
+            check(fn("pb_paged_attention_general_tc")(pool_code, _p(q), _p(k_pool), _p(v_pool), _p(out), _p(block_table),
                                                       block_table.shape[1], _p(ctx.cu_q), _p(ctx.kv_len), _p(slopes), len(q_lens),
                                                       n_q_tiles, hq, hkv, dk, dv, k_stride, v_stride, page_size, float(scale),
-                                                      int(window or 0), int(chunk or 0), keep_first, softcap, _p(sinks), v_share, stream()),
+                                                      int(window or 0), int(chunk or 0), keep_first, softcap, _p(sinks), v_share, out_f32, stream()),
                   "paged_attention_general_tc")
             return
         if insist:
             raise KernelError("paged_attention_general: the tensor-core kernel does not take these sizes or dtypes")
     if tiled is None:
         tiled = GENERAL_TILED
-    if tiled and fn("pb_attention_general_tiled_supported")(code(out.dtype), _p(k_pool), _p(v_pool), hq, hkv, dk, dv, k_stride,
+    if tiled and fn("pb_attention_general_tiled_supported")(pool_code, _p(k_pool), _p(v_pool), hq, hkv, dk, dv, k_stride,
                                                             v_stride):
         group = hq // hkv
         row_tiles = sum(-(-(int(ql) * group) // GENERAL_ROWS) for ql in ctx.host.q_lens)
         n_splits = general_splits(row_tiles * hkv, block_table.shape[1] * page_size)
         partial = ctx.scratch("attn.general.partial", (n * hq * n_splits * (dv + 2),), torch.float32) if n_splits > 1 else None
-        check(fn("pb_paged_attention_general_tiled")(code(out.dtype), _p(q), _p(k_pool), _p(v_pool), _p(out), _p(partial),
+        check(fn("pb_paged_attention_general_tiled")(pool_code, _p(q), _p(k_pool), _p(v_pool), _p(out), _p(partial),
                                                      _p(block_table), block_table.shape[1], _p(ctx.cu_q), _p(ctx.kv_len),
                                                      _p(slopes), n, len(ctx.host.q_lens), row_tiles, n_splits, hq, hkv, dk, dv,
                                                      k_stride, v_stride, page_size, float(scale), int(window or 0),
-                                                     int(chunk or 0), keep_first, softcap, _p(sinks), v_share, stream()),
+                                                     int(chunk or 0), keep_first, softcap, _p(sinks), v_share, out_f32, stream()),
               "paged_attention_general_tiled", kernels=2 if n_splits > 1 else 1)
         return
-    check(fn("pb_paged_attention_general")(code(out.dtype), _p(q), _p(k_pool), _p(v_pool), _p(out), _p(block_table),
+    check(fn("pb_paged_attention_general")(pool_code, _p(q), _p(k_pool), _p(v_pool), _p(out), _p(block_table),
                                            block_table.shape[1], _p(ctx.cu_q), _p(ctx.kv_len), _p(ctx.seq_of_token), _p(slopes),
                                            n, hq, hkv, dk, dv, k_stride, v_stride, page_size, float(scale), int(window or 0),
-                                           int(chunk or 0), keep_first, softcap, _p(sinks), v_share, stream()), "paged_attention_general")
+                                           int(chunk or 0), keep_first, softcap, _p(sinks), v_share, out_f32, stream()), "paged_attention_general")
 
 
 def qkv_split_write(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],

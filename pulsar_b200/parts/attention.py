@@ -212,7 +212,12 @@ class Attention(Mixer):
             ops.qkv_split_write(qkv, q, cache.k_pool if n_kv else None, cache.v_pool if n_kv else None,
                                 cache.slots if n_kv else None, s.n_heads * maps, n_kv * maps, s.head_dim, s.value_dim, cache.page_size,
                                 n_value_heads=n_kv, positions=ctx.positions, q_temperature=s.q_temperature)
-        o = ctx.scratch("attn.o", (n, s.n_heads * maps, s.value_dim))
+        if maps > 1:
+            # float32 rows: the two maps' outputs are subtracted with a weight near one and the difference is normed, which
+            # would magnify a rounding of either by (1 + lambda) / (1 - lambda)
+            o = ctx.scratch("attn.o.maps", (n, s.n_heads * maps, s.value_dim), torch.float32)
+        else:
+            o = ctx.scratch("attn.o", (n, s.n_heads * maps, s.value_dim))
         ops.paged_attention_general(ctx, q, cache.k_pool, cache.v_pool, o, cache.block_table, s.scale, s.window, s.chunk,
                                     self.slopes, keep_first=s.keep_first, softcap=s.softcap, sinks=self.sinks, v_share=maps)
         if maps > 1:

@@ -474,6 +474,41 @@ def test_one_key_that_stands_out_in_either_map(decode, kernel):
 
 
 @gpu
+@pytest.mark.parametrize("kernel", ["tiled", "plain", "tensor_cores"])
+@pytest.mark.parametrize("decode", [False, True])
+def test_maps_from_bfloat16_pages_stay_unrounded_until_they_are_subtracted(decode, kernel):
+    """With a weight near one the difference of the two maps is small beside either, and the norm that follows brings it
+    back to size: a rounding of the maps to bfloat16 would come out about twenty times as large.  All three attention
+    kernels write float32 rows from bfloat16 pages on request."""
+    from pulsar_b200 import ops
+    g = torch.Generator().manual_seed(8)
+    L, H, G, D, V, page = 301, 4, 2, 64, 128, 16
+    R = H // G
+    n_q = 1 if decode else 45
+    lam, eps, gain, scale = 0.9, 1e-6, 0.1, 0.05
+    q = torch.randn(L, H, 2, D, generator=g, dtype=torch.float64)
+    k = torch.randn(L, G, 2, D, generator=g, dtype=torch.float64).bfloat16().double()
+    v = (1.0 + 0.3 * torch.randn(L, G, V, generator=g, dtype=torch.float64)).bfloat16().double()     # both maps near the same mean
+    want = _two_maps(q[L - n_q:], k, v, scale, lam, eps, gain, first=L - n_q)
+    q_eng = q.view(L, G, R, 2, D).permute(0, 1, 3, 2, 4).reshape(L, 2 * H, D)
+    order = list(range(24))
+    random.Random(9).shuffle(order)
+    k_pool, table = _paged(k.reshape(L, 2 * G, D).bfloat16(), page, order)
+    v_pool, _ = _paged(v.bfloat16(), page, order)
+    ctx = _step_context([n_q], [L])
+    errs = {}
+    for maps_dtype in (torch.float32, torch.bfloat16):
+        maps = torch.empty(n_q, 2 * H, V, dtype=maps_dtype, device="cuda")
+        ops.paged_attention_general(ctx, q_eng[L - n_q:].float().cuda().contiguous(), k_pool.cuda(), v_pool.cuda(), maps, table.cuda(),
+                                    scale, tiled=kernel != "plain", tensor_cores=True if kernel == "tensor_cores" else False, v_share=2)
+        out = torch.empty(n_q, H, V, dtype=torch.float32 if maps_dtype == torch.float32 else torch.bfloat16, device="cuda")
+        ops.diff_combine(maps, out, G, lam, eps, gain)
+        errs[maps_dtype] = helpers.rel_err(out.float().cpu(), want)
+    assert errs[torch.float32] < 2e-3, errs
+    assert errs[torch.bfloat16] > 4 * errs[torch.float32], errs
+
+
+@gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_small_kernels_against_their_formulas(dtype):
     from pulsar_b200 import ops
