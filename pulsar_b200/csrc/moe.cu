@@ -19,64 +19,120 @@ namespace {
 
 using namespace pb;
 
-constexpr int kRouteTokens = 4;          // tokens a block of the router shares an expert's row among
+__device__ __forceinline__ void load_chunk(const float* p, float (&f)[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+__device__ __forceinline__ void load_chunk(const __nv_bfloat16* p, float (&f)[8]) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(u[i] << 16); f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u); }
+}
+constexpr int kRouteRows = 4;            // router rows a warp walks side by side: their loads are in flight together
 
-// One block per kRouteTokens tokens; a warp takes an expert (strided), reads its row once, 16 bytes a lane with two
-// chunks in flight, and adds it up against each of the block's tokens.  A token's sums run in an order that depends on
-// the width alone, not on which tokens share its block.
-template <typename T>
+__device__ __forceinline__ void fma4(float& z, const float4& a, const float4& x) {
+    z = fmaf(a.x, x.x, z); z = fmaf(a.y, x.y, z); z = fmaf(a.z, x.z, z); z = fmaf(a.w, x.w, z);
+}
+
+// One block per TOK tokens; a warp takes kRouteRows rows of the router at a time (groups strided over the warps), reads
+// each once, 16 bytes a lane with two chunks per row in flight, and adds it up against each of the block's tokens, whose
+// float32 rows sit in shared memory and are read once for the group's rows.  A token's sums run in an order that depends
+// on the width alone, not on TOK or on which tokens share its block.
+template <typename T, int TOK>
 __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, int* __restrict__ ids,
                                  float* __restrict__ weights, int n, int width, int n_experts, int top, float scale,
                                  int renormalize, int n_extra, float* __restrict__ extra) {
     pdl_wait();
     extern __shared__ __align__(16) float smem[];
-    float* x = smem;                                     // [kRouteTokens][width]
-    float* s = smem + (size_t)kRouteTokens * width;      // [kRouteTokens][n_experts + n_extra]
+    float* x = smem;                                     // [TOK][width]
+    float* s = smem + (size_t)TOK * width;               // [TOK][n_experts + n_extra]
     const int n_rows = n_experts + n_extra;              // the rows behind the experts' compete for nothing: their sigmoids go to `extra`
-    const int t0 = blockIdx.x * kRouteTokens, n_tok = min(kRouteTokens, n - t0);
+    const int t0 = blockIdx.x * TOK, n_tok = min(TOK, n - t0);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-    for (int i = threadIdx.x; i < kRouteTokens * width; i += blockDim.x) {
-        const int tok = i / width;
-        x[i] = tok < n_tok ? to_float(h[(size_t)t0 * width + i]) : 0.0f;
+    constexpr int kPer = 16 / (int)sizeof(T);            // elements of a 16-byte load
+    if (width % kPer == 0 && ((uintptr_t)h & 15) == 0) {
+        const int chunks = width / kPer;
+        for (int i = threadIdx.x; i < TOK * chunks; i += blockDim.x) {
+            const int k = i / chunks, c = i - k * chunks;
+            float f[kPer];
+            if (k < n_tok) {
+                load_chunk(h + (size_t)(t0 + k) * width + c * kPer, f);
+            } else {
+#pragma unroll
+                for (int j = 0; j < kPer; ++j) f[j] = 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < kPer; j += 4)
+                *reinterpret_cast<float4*>(x + k * width + c * kPer + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < TOK; ++k)
+            for (int i = threadIdx.x; i < width; i += blockDim.x)
+                x[k * width + i] = k < n_tok ? to_float(h[(size_t)(t0 + k) * width + i]) : 0.0f;
     }
     __syncthreads();
     const bool vec = (width & 3) == 0 && ((uintptr_t)router & 15) == 0;
-    for (int e = warp; e < n_rows; e += warps) {
-        const float* w = router + (size_t)e * width;
-        float z[kRouteTokens];
+    const int n_groups = (n_rows + kRouteRows - 1) / kRouteRows;
+    for (int grp = warp; grp < n_groups; grp += warps) {
+        const int e0 = grp * kRouteRows;
+        const float* w[kRouteRows];
 #pragma unroll
-        for (int k = 0; k < kRouteTokens; ++k) z[k] = 0.0f;
+        for (int r = 0; r < kRouteRows; ++r) w[r] = router + (size_t)min(e0 + r, n_rows - 1) * width;
+        float z[kRouteRows][TOK];
+#pragma unroll
+        for (int r = 0; r < kRouteRows; ++r)
+#pragma unroll
+            for (int k = 0; k < TOK; ++k) z[r][k] = 0.0f;
         if (vec) {
             int i = lane * 4;
             for (; i + 128 < width; i += 256) {
-                const float4 a = *reinterpret_cast<const float4*>(w + i), b = *reinterpret_cast<const float4*>(w + i + 128);
+                float4 a[kRouteRows], b[kRouteRows];
 #pragma unroll
-                for (int k = 0; k < kRouteTokens; ++k) {
+                for (int r = 0; r < kRouteRows; ++r) {
+                    a[r] = *reinterpret_cast<const float4*>(w[r] + i);
+                    b[r] = *reinterpret_cast<const float4*>(w[r] + i + 128);
+                }
+#pragma unroll
+                for (int k = 0; k < TOK; ++k) {
                     const float4 xa = *reinterpret_cast<const float4*>(x + k * width + i);
                     const float4 xb = *reinterpret_cast<const float4*>(x + k * width + i + 128);
-                    z[k] = fmaf(a.x, xa.x, z[k]); z[k] = fmaf(a.y, xa.y, z[k]); z[k] = fmaf(a.z, xa.z, z[k]); z[k] = fmaf(a.w, xa.w, z[k]);
-                    z[k] = fmaf(b.x, xb.x, z[k]); z[k] = fmaf(b.y, xb.y, z[k]); z[k] = fmaf(b.z, xb.z, z[k]); z[k] = fmaf(b.w, xb.w, z[k]);
+#pragma unroll
+                    for (int r = 0; r < kRouteRows; ++r) { fma4(z[r][k], a[r], xa); fma4(z[r][k], b[r], xb); }
                 }
             }
             if (i < width) {
-                const float4 a = *reinterpret_cast<const float4*>(w + i);
+                float4 a[kRouteRows];
 #pragma unroll
-                for (int k = 0; k < kRouteTokens; ++k) {
+                for (int r = 0; r < kRouteRows; ++r) a[r] = *reinterpret_cast<const float4*>(w[r] + i);
+#pragma unroll
+                for (int k = 0; k < TOK; ++k) {
                     const float4 xa = *reinterpret_cast<const float4*>(x + k * width + i);
-                    z[k] = fmaf(a.x, xa.x, z[k]); z[k] = fmaf(a.y, xa.y, z[k]); z[k] = fmaf(a.z, xa.z, z[k]); z[k] = fmaf(a.w, xa.w, z[k]);
+#pragma unroll
+                    for (int r = 0; r < kRouteRows; ++r) fma4(z[r][k], a[r], xa);
                 }
             }
         } else {
             for (int i = lane; i < width; i += 32) {
-                const float a = w[i];
+                float a[kRouteRows];
 #pragma unroll
-                for (int k = 0; k < kRouteTokens; ++k) z[k] = fmaf(a, x[k * width + i], z[k]);
+                for (int r = 0; r < kRouteRows; ++r) a[r] = w[r][i];
+#pragma unroll
+                for (int k = 0; k < TOK; ++k) {
+                    const float xv = x[k * width + i];
+#pragma unroll
+                    for (int r = 0; r < kRouteRows; ++r) z[r][k] = fmaf(a[r], xv, z[r][k]);
+                }
             }
         }
 #pragma unroll
-        for (int k = 0; k < kRouteTokens; ++k) {
-            const float zk = warp_sum(z[k]);
-            if (lane == 0) s[k * n_rows + e] = 1.0f / (1.0f + expf(-zk));
+        for (int r = 0; r < kRouteRows; ++r) {
+#pragma unroll
+            for (int k = 0; k < TOK; ++k) {
+                const float zk = warp_sum(z[r][k]);
+                if (lane == 0 && e0 + r < n_rows) s[k * n_rows + e0 + r] = 1.0f / (1.0f + expf(-zk));
+            }
         }
     }
     __syncthreads();
@@ -111,16 +167,6 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
     }
 }
 
-__device__ __forceinline__ void load_chunk(const float* p, float (&f)[4]) {
-    const float4 v = *reinterpret_cast<const float4*>(p);
-    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
-}
-__device__ __forceinline__ void load_chunk(const __nv_bfloat16* p, float (&f)[8]) {
-    const uint4 v = *reinterpret_cast<const uint4*>(p);
-    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(u[i] << 16); f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u); }
-}
 template <typename T> struct Chunk;
 template <> struct Chunk<float> { static constexpr int n = 4; };
 template <> struct Chunk<__nv_bfloat16> { static constexpr int n = 8; };
@@ -206,6 +252,37 @@ __global__ void moe_down_kernel(const T* __restrict__ act, const T* __restrict__
     }
 }
 
+template <typename T, int TOK>
+int launch_route(const void* h, const float* router, int* ids, float* weights, int n, int width, int n_experts, int top, float scale,
+                 int renormalize, int n_extra, float* extra, cudaStream_t stream) {
+    const size_t smem = sizeof(float) * TOK * ((size_t)width + n_experts + n_extra);
+    if (smem > 200 * 1024) return PB_ERR_TOO_LARGE;
+    static size_t allowed = 48 * 1024;
+    if (smem > allowed) {
+        const cudaError_t ce = cudaFuncSetAttribute(moe_route_kernel<T, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (ce != cudaSuccess) return (int)ce;
+        allowed = smem;
+    }
+    int warps = (n_experts + n_extra + kRouteRows - 1) / kRouteRows;      // a warp per group of rows where that fits a block
+    if (warps > 16) warps = 16;
+    if (warps < TOK) warps = TOK;                                         // warp k picks for token k
+    return launch_pdl(moe_route_kernel<T, TOK>, dim3((n + TOK - 1) / TOK), dim3(32 * warps), smem, stream, (const T*)h, router, ids,
+                      weights, n, width, n_experts, top, scale, renormalize, n_extra, extra);
+}
+
+template <typename T>
+int dispatch_route(const void* h, const float* router, int* ids, float* weights, int n, int width, int n_experts, int top, float scale,
+                   int renormalize, int n_extra, float* extra, cudaStream_t stream) {
+    // tokens a block shares the router's rows among: one where the step is a few tokens (their blocks run side by side),
+    // eight where their float32 rows leave room for three blocks on a SM, else four
+    const size_t row = sizeof(float) * ((size_t)width + n_experts + n_extra);
+#define PB_ROUTE(TOK) return launch_route<T, TOK>(h, router, ids, weights, n, width, n_experts, top, scale, renormalize, n_extra, extra, stream)
+    if (n <= 16) PB_ROUTE(1);
+    if (8 * row <= 72 * 1024) PB_ROUTE(8);
+    PB_ROUTE(4);
+#undef PB_ROUTE
+}
+
 }  // namespace
 
 // router [n_experts + n_extra, width]: the rows behind the experts' are scored too (sigmoid) and go to extra [n, n_extra].
@@ -213,27 +290,9 @@ PB_EXPORT int pb_moe_route(int dtype, const void* h, const float* router, int* i
                            int top, float scale, int renormalize, int n_extra, float* extra, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (width <= 0 || n_experts <= 0 || top <= 0 || top > n_experts || n_extra < 0 || (n_extra > 0 && extra == nullptr)) return PB_ERR_BAD_SIZE;
-    const size_t smem = sizeof(float) * kRouteTokens * ((size_t)width + n_experts + n_extra);
-    if (smem > 200 * 1024) return PB_ERR_TOO_LARGE;
-    int threads = 32 * (n_experts + n_extra);             // a warp per row where that fits a block
-    if (threads > 1024) threads = 1024;
-    if (threads < 32 * kRouteTokens) threads = 32 * kRouteTokens;
-    const int blocks = (n + kRouteTokens - 1) / kRouteTokens;
-    cudaError_t ce = cudaSuccess;
-    if (dtype == PB_F32) {
-        static size_t allowed = 48 * 1024;
-        if (smem > allowed) { ce = cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed = smem; }
-        if (ce != cudaSuccess) return (int)ce;
-        return launch_pdl(moe_route_kernel<float>, dim3(blocks), dim3(threads), smem, stream, (const float*)h, router, ids, weights, n,
-                          width, n_experts, top, scale, renormalize, n_extra, extra);
-    }
-    if (dtype == PB_BF16) {
-        static size_t allowed = 48 * 1024;
-        if (smem > allowed) { ce = cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed = smem; }
-        if (ce != cudaSuccess) return (int)ce;
-        return launch_pdl(moe_route_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), smem, stream, (const __nv_bfloat16*)h, router, ids,
-                          weights, n, width, n_experts, top, scale, renormalize, n_extra, extra);
-    }
+    if (dtype == PB_F32) return dispatch_route<float>(h, router, ids, weights, n, width, n_experts, top, scale, renormalize, n_extra, extra, stream);
+    if (dtype == PB_BF16)
+        return dispatch_route<__nv_bfloat16>(h, router, ids, weights, n, width, n_experts, top, scale, renormalize, n_extra, extra, stream);
     return PB_ERR_BAD_DTYPE;
 }
 
