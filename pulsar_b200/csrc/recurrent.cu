@@ -8,9 +8,10 @@
 //                  do not depend on the recurrence and are kept in flight eight at a time.
 //   min_gru_chunked  the same for long portions, parallel over tokens: a portion is cut into runs of kRun tokens; pass 1
 //                  gives every (run, channel) its decay product A = prod (1 - z') and its contribution B (the state the run
-//                  would leave from zero); pass 2 walks a sequence's runs in order, S_in(run) kept per run, and leaves the
-//                  final state; pass 3 walks every run again from its S_in and writes y.  The state entering a run is
-//                  A * S + B folded in run order, so a token's value differs from the token-by-token one by rounding only.
+//                  would leave from zero); pass 2 folds a sequence's runs in order (in segments, a warp each, joined through
+//                  shared memory), keeps S_in(run) per run and leaves the final state; pass 3 walks every run again from
+//                  its S_in and writes y.  The state entering a run is A * S + B folded over the runs before it, so a
+//                  token's value differs from the token-by-token one by rounding only.
 #include "common.cuh"
 
 namespace {
@@ -110,34 +111,66 @@ __global__ void min_gru_runs_kernel(const float* __restrict__ proj, const float*
     run_b[(size_t)blockIdx.y * W + c] = B;
 }
 
-// per (sequence, channel): the state that enters each of the sequence's runs (written over run_b), and the final state
-__global__ void min_gru_carry_kernel(float* __restrict__ run_a, float* __restrict__ run_b, float* __restrict__ state,
-                                     long state_stride, const int* __restrict__ cu_q, const int* __restrict__ state_slots, int W) {
+// per (sequence, channel): the state that enters each of the sequence's runs (written over run_b), and the final state.
+// A block takes 32 channels (a lane each) and cuts the sequence's runs into kCarryWarps segments, a warp each: the warp
+// folds its segment from (1, 0) with all its loads in flight, the segments' products meet in shared memory, every warp
+// folds the ones before it onto the kept state, and walks its segment again from there.  The first kCarryKeep runs of a
+// segment stay in registers between the two walks (portions up to kCarryWarps * kCarryKeep runs: all of them).
+constexpr int kCarryWarps = 8, kCarryKeep = 16;
+
+__global__ void __launch_bounds__(kCarryWarps * 32)
+min_gru_carry_kernel(const float* __restrict__ run_a, float* __restrict__ run_b, float* __restrict__ state, long state_stride,
+                     const int* __restrict__ cu_q, const int* __restrict__ state_slots, int W) {
     pdl_wait();
-    const int c = blockIdx.x * blockDim.x + threadIdx.x, s = blockIdx.y;
-    if (c >= W) return;
+    __shared__ float As[kCarryWarps][32], Bs[kCarryWarps][32];
+    const int lane = threadIdx.x & 31, j = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + lane, s = blockIdx.y;
+    const bool on = c < W;
     int run0 = 0;
     for (int k = 0; k < s; ++k) run0 += (cu_q[k + 1] - cu_q[k] + kRun - 1) / kRun;
     const int runs = (cu_q[s + 1] - cu_q[s] + kRun - 1) / kRun;
+    const int seg = (runs + kCarryWarps - 1) / kCarryWarps;
+    const int r0 = min(j * seg, runs), r1 = min(r0 + seg, runs);
     float* kept = state + (size_t)state_slots[s] * state_stride + c;
-    float S = *kept;
-    constexpr int U = 16;       // the runs' products do not depend on the fold: sixteen runs' loads in flight
-    for (int r = 0; r < runs; r += U) {
-        float A[U], B[U];
+    float A[kCarryKeep], B[kCarryKeep];
+    float a_seg = 1.0f, b_seg = 0.0f, S = 0.0f;
+    if (on) {
+        S = *kept;
 #pragma unroll
-        for (int k = 0; k < U; ++k) {
-            const size_t at = (size_t)(run0 + (r + k < runs ? r + k : r)) * W + c;
-            A[k] = run_a[at]; B[k] = run_b[at];
-        }
-#pragma unroll
-        for (int k = 0; k < U; ++k) {
-            if (r + k < runs) {
-                run_b[(size_t)(run0 + r + k) * W + c] = S;
-                S = A[k] * S + B[k];
+        for (int k = 0; k < kCarryKeep; ++k) {
+            if (r0 + k < r1) {
+                const size_t at = (size_t)(run0 + r0 + k) * W + c;
+                A[k] = run_a[at]; B[k] = run_b[at];
             }
         }
+#pragma unroll
+        for (int k = 0; k < kCarryKeep; ++k)
+            if (r0 + k < r1) { a_seg *= A[k]; b_seg = A[k] * b_seg + B[k]; }
+#pragma unroll 4
+        for (int r = r0 + kCarryKeep; r < r1; ++r) {
+            const size_t at = (size_t)(run0 + r) * W + c;
+            const float a = run_a[at], b = run_b[at];
+            a_seg *= a; b_seg = a * b_seg + b;
+        }
     }
-    *kept = S;
+    As[j][lane] = a_seg; Bs[j][lane] = b_seg;
+    __syncthreads();                                       // every warp has read the kept state by now
+    if (!on) return;
+    for (int jj = 0; jj < j; ++jj) S = As[jj][lane] * S + Bs[jj][lane];
+#pragma unroll
+    for (int k = 0; k < kCarryKeep; ++k) {
+        if (r0 + k < r1) {
+            run_b[(size_t)(run0 + r0 + k) * W + c] = S;
+            S = A[k] * S + B[k];
+        }
+    }
+    for (int r = r0 + kCarryKeep; r < r1; ++r) {
+        const size_t at = (size_t)(run0 + r) * W + c;
+        const float a = run_a[at], b = run_b[at];
+        run_b[at] = S;
+        S = a * S + b;
+    }
+    if (j == kCarryWarps - 1) *kept = S;                   // the last warp's walk ends at the sequence's end, whatever its share
 }
 
 template <typename T>
@@ -196,8 +229,8 @@ PB_EXPORT int pb_min_gru(int dtype, const float* proj, const float* bz, const fl
     const dim3 grid_r((W + threads - 1) / threads, max_runs);
     int rc = launch_pdl(min_gru_runs_kernel, grid_r, block, 0, stream, proj, bz, bx, cu_q, n_seqs, run_a, run_b, W);
     if (rc != 0) return rc;
-    // the fold is a chain of a few dependent steps per channel: warps of their own, spread over the SMs
-    rc = launch_pdl(min_gru_carry_kernel, dim3((W + 31) / 32, n_seqs), dim3(32), 0, stream, run_a, run_b, state, state_stride, cu_q, state_slots, W);
+    rc = launch_pdl(min_gru_carry_kernel, dim3((W + 31) / 32, n_seqs), dim3(kCarryWarps * 32), 0, stream, (const float*)run_a, run_b, state,
+                    state_stride, cu_q, state_slots, W);
     if (rc != 0) return rc;
     if (dtype == PB_F32)
         return launch_pdl(min_gru_outputs_kernel<float>, grid_r, block, 0, stream, proj, bz, bx, cu_q, n_seqs, (const float*)run_b, (float*)y, W);
