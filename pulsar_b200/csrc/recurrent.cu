@@ -18,15 +18,24 @@ namespace {
 
 using namespace pb;
 
-// the exponential is the library's; the reciprocal is the special-function unit's (two units in the last place, and exactly 0
-// where 1 + e^-v has left its range): the kernels below spend most of their instructions on these
-__device__ __forceinline__ float sigmoidf(float v) { return __fdividef(1.0f, 1.0f + expf(-v)); }
-
-__device__ __forceinline__ void gru_gates(float z, float u, float bz, float bx, float& zz, float& cand) {
-    zz = sigmoidf(z + bz);
-    const float uu = u + bx;
-    cand = uu >= 0.0f ? uu + 0.5f : sigmoidf(uu);
+// FAST (the bfloat16 engine): exponential and reciprocal from the special-function unit (ex2.approx of v log2 e and
+// rcp.approx: a few units in the last place of a float32 each, and exactly 0 or 1 where e^-v leaves its range); the kernels
+// below spend most of their instructions on these.  The float32 engine keeps the library's exponential and a true division.
+template <bool FAST>
+__device__ __forceinline__ float sigmoid_of(float v) {
+    if (FAST) return __fdividef(1.0f, 1.0f + __expf(-v));
+    return 1.0f / (1.0f + expf(-v));
 }
+
+template <bool FAST>
+__device__ __forceinline__ void gru_gates(float z, float u, float bz, float bx, float& zz, float& cand) {
+    zz = sigmoid_of<FAST>(z + bz);
+    const float uu = u + bx;
+    cand = uu >= 0.0f ? uu + 0.5f : sigmoid_of<FAST>(uu);
+}
+
+template <typename T> struct Fast { static constexpr bool value = false; };
+template <> struct Fast<__nv_bfloat16> { static constexpr bool value = true; };
 
 template <typename T>
 __global__ void min_gru_kernel(const float* __restrict__ proj, const float* __restrict__ bz, const float* __restrict__ bx,
@@ -52,9 +61,9 @@ __global__ void min_gru_kernel(const float* __restrict__ proj, const float* __re
         for (int k = 0; k < U; ++k) {
             if (t + k < t1) {
                 float zz, cand;
-                gru_gates(z[k], u[k], b_z, b_x, zz, cand);
+                gru_gates<Fast<T>::value>(z[k], u[k], b_z, b_x, zz, cand);
                 S = (1.0f - zz) * S + zz * cand;
-                y[(size_t)(t + k) * W + c] = from_float<T>(S * (g[k] * sigmoidf(g[k])));
+                y[(size_t)(t + k) * W + c] = from_float<T>(S * (g[k] * sigmoid_of<Fast<T>::value>(g[k])));
             }
         }
     }
@@ -80,6 +89,7 @@ __device__ __forceinline__ bool find_run(const int* cu_q, int n_seqs, int run, i
     return false;
 }
 
+template <bool FAST>
 __global__ void min_gru_runs_kernel(const float* __restrict__ proj, const float* __restrict__ bz, const float* __restrict__ bx,
                                     const int* __restrict__ cu_q, int n_seqs, float* __restrict__ run_a, float* __restrict__ run_b,
                                     int W) {
@@ -101,7 +111,7 @@ __global__ void min_gru_runs_kernel(const float* __restrict__ proj, const float*
         for (int k = 0; k < U; ++k) {
             if (t + k < t1) {
                 float zz, cand;
-                gru_gates(z[k], u[k], b_z, b_x, zz, cand);
+                gru_gates<FAST>(z[k], u[k], b_z, b_x, zz, cand);
                 A = (1.0f - zz) * A;
                 B = (1.0f - zz) * B + zz * cand;
             }
@@ -195,9 +205,9 @@ __global__ void min_gru_outputs_kernel(const float* __restrict__ proj, const flo
         for (int k = 0; k < U; ++k) {
             if (t + k < t1) {
                 float zz, cand;
-                gru_gates(z[k], u[k], b_z, b_x, zz, cand);
+                gru_gates<Fast<T>::value>(z[k], u[k], b_z, b_x, zz, cand);
                 S = (1.0f - zz) * S + zz * cand;
-                y[(size_t)(t + k) * W + c] = from_float<T>(S * (g[k] * sigmoidf(g[k])));
+                y[(size_t)(t + k) * W + c] = from_float<T>(S * (g[k] * sigmoid_of<Fast<T>::value>(g[k])));
             }
         }
     }
@@ -227,7 +237,8 @@ PB_EXPORT int pb_min_gru(int dtype, const float* proj, const float* bz, const fl
     }
     if (run_a == nullptr || run_b == nullptr) return PB_ERR_BAD_SIZE;
     const dim3 grid_r((W + threads - 1) / threads, max_runs);
-    int rc = launch_pdl(min_gru_runs_kernel, grid_r, block, 0, stream, proj, bz, bx, cu_q, n_seqs, run_a, run_b, W);
+    int rc = dtype == PB_F32 ? launch_pdl(min_gru_runs_kernel<false>, grid_r, block, 0, stream, proj, bz, bx, cu_q, n_seqs, run_a, run_b, W)
+                             : launch_pdl(min_gru_runs_kernel<true>, grid_r, block, 0, stream, proj, bz, bx, cu_q, n_seqs, run_a, run_b, W);
     if (rc != 0) return rc;
     rc = launch_pdl(min_gru_carry_kernel, dim3((W + 31) / 32, n_seqs), dim3(kCarryWarps * 32), 0, stream, (const float*)run_a, run_b, state,
                     state_stride, cu_q, state_slots, W);
