@@ -109,14 +109,14 @@ def megusun_work(z: dict, phase: str) -> Dict[str, Tuple[float, float, str]]:
     steps = 1 if phase == "prefill" else 4
     pairs = seqs * _pairs(n // seqs, start)
     keys_read = seqs * (start + n // seqs)
-    attention = (La * (keys_read * (2 * G * D + G * V) * 2 + n * 2 * H * (D * 4 + V * 2)), La * 2.0 * 2 * H * 2 * (D + V) * pairs)
+    attention = (La * (keys_read * (2 * G * D + G * V) * 2 + n * 2 * H * (D * 4 + V * 4)), La * 2.0 * 2 * H * 2 * (D + V) * pairs)      # float32 queries in, float32 maps out
     distinct = E * (1.0 - (1.0 - top / E) ** n)
     work = {
         "paged_attention_general_tc": (attention[0], attention[1], "bf16 tensor"),
         "paged_attention_general_tiled": (attention[0], attention[1], "fp32 FMA"),
         "paged_attention_general": (attention[0], attention[1], "fp32 FMA"),
         "qkv_split_write": (La * n * (2 * H * D * (2 + 4) + (2 * G * D + G * V) * 4), 0.0, ""),
-        "diff_combine": (La * n * H * V * (2 * 2 + 2), 0.0, ""),
+        "diff_combine": (La * n * H * V * (2 * 4 + 2), 0.0, ""),                       # two float32 maps in, one head out
         "norm_shift": (n * w * (4 + 2 + 2), 0.0, ""),                                  # the first layer's; the others' ride in parallel_add
         "parallel_add": (n * w * ((L - 1) * (4 + 2 + 2 + 4 + 2 + 2) + (4 + 2 + 2 + 4)), 0.0, ""),
         "activation": (Ld * n * z["ff"] * (4 + 2), 0.0, ""),
