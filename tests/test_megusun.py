@@ -618,10 +618,11 @@ def test_small_kernels_against_their_formulas(dtype):
 
 @gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("q_lens", [[1, 1, 1], [7, 1, 30], [150, 2, 65, 33], [64], [97]])
+@pytest.mark.parametrize("q_lens", [[1, 1, 1], [7, 1, 30], [150, 2, 65, 33], [64], [97], [2200, 3, 700]])
 def test_the_recurrence_against_its_formula(q_lens, dtype):
     """Both forms of the kernel (token by token; in runs, parallel over tokens) with kept states in slots out of order, and
-    a second step that goes on from the states the first one left."""
+    a second step that goes on from the states the first one left.  The longest portion has more runs than a block's
+    warps keep in registers between their two walks."""
     from pulsar_b200 import ops
     g = torch.Generator().manual_seed(sum(q_lens))
     W, n = 72, sum(q_lens)
