@@ -73,6 +73,8 @@ def topunex_config(z: dict) -> dict:
 # a head of 128); the feed-forwards alternate between a dense one and 32 experts of which a token uses 4, beside a gated
 # shared expert.  The shape also carries what the model beside it needs (Topunex: a window, kept keys, rotating dimensions).
 MEGUSUN_SIZES = {
+    "1k": dict(width=1024, layers=8, heads=8, kv_heads=2, dim=128, map_dim=64, vdim=128, gru=1024, rot=64, window=1024, keep=4,
+               ff=4096, experts=16, top=2, expert_ff=512, shared_ff=1024, vocab=32000),
     "2k": dict(width=2048, layers=8, heads=16, kv_heads=4, dim=128, map_dim=64, vdim=128, gru=2048, rot=64, window=1024, keep=4,
                ff=8192, experts=32, top=4, expert_ff=1024, shared_ff=2048, vocab=32000),
     "4k": dict(width=4096, layers=8, heads=32, kv_heads=8, dim=128, map_dim=64, vdim=128, gru=4096, rot=64, window=1024, keep=4,
