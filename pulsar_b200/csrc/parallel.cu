@@ -84,32 +84,47 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
 }
 __device__ __forceinline__ float dot4(float4 v) { return v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
 
-constexpr int kVecIters = 4;            // a thread holds up to 4 x 4 elements of a row: widths up to 4 * 512 * 4
+// two sums over the block with one pair of barriers; each is added up in block_sum's order.  `scratch` needs 64 floats.
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    a = warp_sum(a);
+    b = warp_sum(b);
+    __syncthreads();   // scratch may still be read from an earlier call
+    if (lane == 0) { scratch[warp] = a; scratch[32 + warp] = b; }
+    __syncthreads();
+    a = warp_sum(lane < nwarps ? scratch[lane] : 0.0f);
+    b = warp_sum(lane < nwarps ? scratch[32 + lane] : 0.0f);
+}
+
+constexpr int kVecIters = 4;            // a thread holds up to 4 x 4 elements of a row: widths up to 4 * 512 * 4.  The kernels take
+                                        // the count as ITERS (1, 2 or 4, by the width) so that narrow rows cost few registers.
 
 // norm_shift_row with the row in registers.  `cur` holds the thread's part of row t on entry (the caller loaded it, and may
 // have stored it as the new stream); the row above is loaded here through `row.at4`.
-template <typename T, typename Row>
-__device__ __forceinline__ void norm_shift_row4(const Row& row, int t, const float4 (&cur)[kVecIters], const ShiftArgs& p,
+template <typename T, int ITERS, typename Row>
+__device__ __forceinline__ void norm_shift_row4(const Row& row, int t, const float4 (&cur)[ITERS], const ShiftArgs& p,
                                                 T* __restrict__ h_out, T* __restrict__ hs_out, int width, float* scratch) {
     const int s = p.seq_of_token[t];
     const int first = p.cu_q[s], last = p.cu_q[s + 1] - 1;
     const bool has_prev = p.shift != nullptr && t > first;
     const int quads = width >> 2;
-    float4 prev[kVecIters];
+    float4 prev[ITERS];
     float ss = 0.0f, ssp = 0.0f;
 #pragma unroll
-    for (int k = 0; k < kVecIters; ++k) {
+    for (int k = 0; k < ITERS; ++k) {
         const int q = threadIdx.x + k * blockDim.x;
         if (q < quads) {
             ss += dot4(cur[k]);
             if (has_prev) { prev[k] = row.at4(t - 1, q); ssp += dot4(prev[k]); }
         }
     }
-    const float inv = rsqrtf(block_sum(ss, scratch) / (float)width + p.eps);
-    const float invp = has_prev ? rsqrtf(block_sum(ssp, scratch) / (float)width + p.eps) : 0.0f;
+    block_sum2(ss, ssp, scratch);
+    const float inv = rsqrtf(ss / (float)width + p.eps);
+    const float invp = has_prev ? rsqrtf(ssp / (float)width + p.eps) : 0.0f;
     const float* kept = p.state + (size_t)p.state_slots[s] * p.state_stride;
 #pragma unroll
-    for (int k = 0; k < kVecIters; ++k) {
+    for (int k = 0; k < ITERS; ++k) {
         const int q = threadIdx.x + k * blockDim.x;
         if (q < quads) {
             const size_t at = (size_t)t * width + 4 * q;
@@ -144,19 +159,19 @@ __global__ void norm_shift_kernel(const float* __restrict__ x, const ShiftArgs p
     norm_shift_row<T>(PlainRow{x, width}, blockIdx.x, p, h_out, hs_out, width, scratch);
 }
 
-template <typename T>
+template <typename T, int ITERS>
 __global__ void norm_shift4_kernel(const float* __restrict__ x, const ShiftArgs p, T* __restrict__ h_out, T* __restrict__ hs_out,
                                    int width) {
     pdl_wait();
-    __shared__ float scratch[32];
+    __shared__ float scratch[64];
     const PlainRow row{x, width};
-    float4 cur[kVecIters];
+    float4 cur[ITERS];
 #pragma unroll
-    for (int k = 0; k < kVecIters; ++k) {
+    for (int k = 0; k < ITERS; ++k) {
         const int q = threadIdx.x + k * blockDim.x;
         if (q < (width >> 2)) cur[k] = row.at4(blockIdx.x, q);
     }
-    norm_shift_row4<T>(row, blockIdx.x, cur, p, h_out, hs_out, width, scratch);
+    norm_shift_row4<T, ITERS>(row, blockIdx.x, cur, p, h_out, hs_out, width, scratch);
 }
 
 template <typename T>
@@ -209,17 +224,17 @@ __global__ void parallel_add_kernel(const float* __restrict__ x, const T* __rest
     if (next.weight != nullptr) norm_shift_row<T>(row, t, next, h_out, hs_out, width, scratch);
 }
 
-template <typename T>
+template <typename T, int ITERS>
 __global__ void parallel_add4_kernel(const float* __restrict__ x, const T* __restrict__ a, const T* __restrict__ b, float m,
                                      float* __restrict__ x_out, const CommitArgs c, const ShiftArgs next, T* __restrict__ h_out,
                                      T* __restrict__ hs_out, int width) {
     pdl_wait();
-    __shared__ float scratch[32];
+    __shared__ float scratch[64];
     const int t = blockIdx.x, quads = width >> 2;
     const SumRow<T> row{x, a, b, m, width};
-    float4 cur[kVecIters];
+    float4 cur[ITERS];
 #pragma unroll
-    for (int k = 0; k < kVecIters; ++k) {
+    for (int k = 0; k < ITERS; ++k) {
         const int q = threadIdx.x + k * blockDim.x;
         if (q < quads) {
             cur[k] = row.at4(t, q);
@@ -233,7 +248,7 @@ __global__ void parallel_add4_kernel(const float* __restrict__ x, const T* __res
             for (int q = threadIdx.x; q < quads; q += blockDim.x) store4(kept + 4 * q, load4(c.pending + (size_t)s * width + 4 * q));
         }
     }
-    if (next.weight != nullptr) norm_shift_row4<T>(row, t, cur, next, h_out, hs_out, width, scratch);
+    if (next.weight != nullptr) norm_shift_row4<T, ITERS>(row, t, cur, next, h_out, hs_out, width, scratch);
 }
 
 __device__ __forceinline__ float act_value(float z, int kind) {
@@ -254,6 +269,12 @@ int row_threads(int width) {
     int threads = (width + 3) / 4;
     threads = (threads + 31) / 32 * 32;
     return threads > 512 ? 512 : (threads < 32 ? 32 : threads);
+}
+
+// quads of a row that a thread of the four-at-a-time form holds: 1, 2 or kVecIters
+int vector_iters(int width, int threads) {
+    const int per_thread = ((width >> 2) + threads - 1) / threads;
+    return per_thread <= 1 ? 1 : (per_thread <= 2 ? 2 : kVecIters);
 }
 
 bool aligned16(const void* p) { return p == nullptr || ((uintptr_t)p & 15) == 0; }
@@ -279,11 +300,13 @@ PB_EXPORT int pb_norm_shift(int dtype, const float* x, const float* weight, floa
     if (shift != nullptr && (state == nullptr || state_slots == nullptr || pending == nullptr || hs == nullptr)) return PB_ERR_BAD_SIZE;
     const ShiftArgs p{weight, shift, state, state_stride, seq_of_token, cu_q, state_slots, pending, eps};
     if (vector_rows(width, state_stride, 0, {x, weight, shift, state, h, hs, pending})) {
-        if (dtype == PB_F32)
-            return launch_pdl(norm_shift4_kernel<float>, dim3(n), dim3(row_threads(width)), 0, stream, x, p, (float*)h, (float*)hs, width);
-        if (dtype == PB_BF16)
-            return launch_pdl(norm_shift4_kernel<__nv_bfloat16>, dim3(n), dim3(row_threads(width)), 0, stream, x, p, (__nv_bfloat16*)h,
-                              (__nv_bfloat16*)hs, width);
+        const int threads = row_threads(width), iters = vector_iters(width, threads);
+#define PB_SHIFT4(T, ITERS) return launch_pdl(norm_shift4_kernel<T, ITERS>, dim3(n), dim3(threads), 0, stream, x, p, (T*)h, (T*)hs, width)
+#define PB_SHIFT4_BY_ITERS(T) do { if (iters == 1) PB_SHIFT4(T, 1); if (iters == 2) PB_SHIFT4(T, 2); PB_SHIFT4(T, kVecIters); } while (0)
+        if (dtype == PB_F32) PB_SHIFT4_BY_ITERS(float);
+        if (dtype == PB_BF16) PB_SHIFT4_BY_ITERS(__nv_bfloat16);
+#undef PB_SHIFT4_BY_ITERS
+#undef PB_SHIFT4
         return PB_ERR_BAD_DTYPE;
     }
     if (dtype == PB_F32)
@@ -311,13 +334,15 @@ PB_EXPORT int pb_parallel_add(int dtype, const float* x, const void* a, const vo
     const ShiftArgs nx{next_weight, next_shift, next_state, next_state_stride, seq_of_token, cu_q, state_slots, next_pending, next_eps};
     if (vector_rows(width, state_stride, next_state_stride, {x, a, b, x_out, pending, state, next_weight, next_shift, next_state,
                                                              next_pending, h, hs})) {
-        if (dtype == PB_F32)
-            return launch_pdl(parallel_add4_kernel<float>, dim3(n), dim3(row_threads(width)), 0, stream, x, (const float*)a,
-                              (const float*)b, m, x_out, c, nx, (float*)h, (float*)hs, width);
-        if (dtype == PB_BF16)
-            return launch_pdl(parallel_add4_kernel<__nv_bfloat16>, dim3(n), dim3(row_threads(width)), 0, stream, x,
-                              (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, m, x_out, c, nx, (__nv_bfloat16*)h, (__nv_bfloat16*)hs,
-                              width);
+        const int threads = row_threads(width), iters = vector_iters(width, threads);
+#define PB_ADD4(T, ITERS) \
+    return launch_pdl(parallel_add4_kernel<T, ITERS>, dim3(n), dim3(threads), 0, stream, x, (const T*)a, (const T*)b, m, x_out, c, nx, \
+                      (T*)h, (T*)hs, width)
+#define PB_ADD4_BY_ITERS(T) do { if (iters == 1) PB_ADD4(T, 1); if (iters == 2) PB_ADD4(T, 2); PB_ADD4(T, kVecIters); } while (0)
+        if (dtype == PB_F32) PB_ADD4_BY_ITERS(float);
+        if (dtype == PB_BF16) PB_ADD4_BY_ITERS(__nv_bfloat16);
+#undef PB_ADD4_BY_ITERS
+#undef PB_ADD4
         return PB_ERR_BAD_DTYPE;
     }
     if (dtype == PB_F32)
