@@ -29,6 +29,12 @@ class PositionSpec:
     # (factor, low, high, original): frequencies are rescaled by wavelength l = 2 pi / f: kept where l < original / high,
     # divided by factor where l > original / low, and blended linearly in original / l between the two.  None: as they are.
     scaling: Optional[Tuple[float, float, float, float]] = None
+    divide: Optional[float] = None   # every frequency is divided by this
+    # (factor, original, fast, slow): pair i keeps its frequency below a ramp over the pair numbers, has it divided by factor
+    # above it and a linear blend on it; the ramp runs from floor(pair(fast)) (at least 0) to ceil(pair(slow)) (at most
+    # rotary_dim - 1), pair(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta), and is at least 0.001 long.
+    ramp: Optional[Tuple[float, float, float, float]] = None
+    magnitude: float = 1.0           # cosines and sines are multiplied by this
 
 
 @dataclass(frozen=True)
@@ -52,6 +58,7 @@ class MixerSpec:
     keep_first: int = 0              # with a window or chunk: the first keep_first keys of a sequence stay visible all the same
     softcap: Optional[float] = None  # c: the scaled score becomes c * tanh(score / c)
     sinks: bool = False              # a learned number per head whose exponential joins the softmax's denominator (no key, no value)
+    fixed_sink: Optional[float] = None   # the same with one given number for all heads instead of a learned tensor (0: one is added)
     bias: bool = False               # the q, k, v and o projections have biases (the weight's name + ".b" unless named by role)
     output_gate: bool = False        # the concatenated heads are multiplied by sigmoid(W_g h) before the output projection
     values_from_keys: bool = False   # no v projection: the value is the key as projected (before rotation and norm)
@@ -121,6 +128,19 @@ class LayerCall:
     block: int
     cache: int
     state: Optional[int] = None      # a further cache entry, of kind "state", that belongs to the block itself (``Block.state_need``)
+    members: Tuple[int, ...] = ()    # a composite mixer: the cache entries of its members behind the first (``Mixer.member_needs``)
+    opens: Optional[int] = None      # t: this call opens walk number t over a run of layers (``ModelSpec.walk``)
+
+
+@dataclass(frozen=True)
+class WalkSpec:
+    """A run of layers that is walked several times in a row with the same weights (the run order names the blocks once per
+    walk, each time with cache entries of its own).  Right before the first layer of walk t (``LayerCall.opens`` = t; the
+    first walk too) the stream becomes x <- W [x ; x0] + step[t]: x0 the embedding rows, W the tensor ``in_name``
+    [width, 2 width] (the stream's columns first), step the tensor ``step_name`` [times, width]."""
+    in_name: str
+    step_name: str
+    times: int
 
 
 @dataclass(frozen=True)
@@ -143,9 +163,10 @@ class ModelSpec:
     logit_softcap: Optional[float] = None         # ... and then capped: cap * tanh(logits / cap)
     position_axes: int = 1                        # axes of a token's position; axis 0 is its index in the sequence
     ignore: Tuple[str, ...] = ()                  # tensor-name patterns (fnmatch) that a folder may hold and nobody reads
+    walk: Optional["WalkSpec"] = None             # a run of layers walked several times, and what opens each walk
 
     @property
     def n_cache_entries(self) -> int:
         if not self.run_order:
             return 0
-        return 1 + max(max(call.cache, -1 if call.state is None else call.state) for call in self.run_order)
+        return 1 + max(max(call.cache, -1 if call.state is None else call.state, *call.members) for call in self.run_order)

@@ -164,7 +164,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
 // so the rounding of the argument never grows with the position.  (The reference reduces by whole
 // quadrants and picks among four cases: pulsar-core/src/kernels/rope_common.cuh:19-43.)
 __global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ quadrants_per_position,
-                                  float* __restrict__ cos_out, float* __restrict__ sin_out, int half) {
+                                  float* __restrict__ cos_out, float* __restrict__ sin_out, int half, float magnitude) {
     const int t = blockIdx.x;
     const double p = (double)positions[t];
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
@@ -174,8 +174,8 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const doubl
         if (folded) r = copysign(1.0, r) - r;
         float si, co;
         sincospif((float)r, &si, &co);
-        cos_out[(size_t)t * half + j] = folded ? -co : co;
-        sin_out[(size_t)t * half + j] = si;
+        cos_out[(size_t)t * half + j] = (folded ? -co : co) * magnitude;
+        sin_out[(size_t)t * half + j] = si * magnitude;
     }
 }
 
@@ -533,11 +533,11 @@ PB_EXPORT int pb_add_rmsnorm(int dtype, float* residual, const void* delta, cons
 }
 
 PB_EXPORT int pb_rope_table(const int* positions, const double* quadrants_per_position, float* cos_out, float* sin_out,
-                            int n, int half, cudaStream_t stream) {
+                            int n, int half, float magnitude, cudaStream_t stream) {
     if (n <= 0 || half <= 0) return 0;
     int b = 32;
     while (b < half && b < 256) b <<= 1;
-    rope_table_kernel<<<n, b, 0, stream>>>(positions, quadrants_per_position, cos_out, sin_out, half);
+    rope_table_kernel<<<n, b, 0, stream>>>(positions, quadrants_per_position, cos_out, sin_out, half, magnitude);
     return launch_status();
 }
 

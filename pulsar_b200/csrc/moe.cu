@@ -3,6 +3,8 @@
 //   moe_route      z = W_r h in float32 (W_r float32 [E, width]; h in the activation dtype), s = sigmoid(z), the `top`
 //                  largest s per token (ties: the lower index), weights s * scale, or with `renormalize` s / sum of the
 //                  chosen s * scale.  ids int32 [N, top] in descending order of s, weights float32 [N, top].
+//                  With `softmax` the scores are s = softmax(z) over all experts instead, and a renormalised weight is
+//                  s / (sum of the chosen s + renorm_eps) * scale.
 //   moe_gate_up    for every (token, chosen expert): g = W_gate[e] h, u = W_up[e] h (float32 sums), the gated unit
 //                  out = g' * sigmoid(alpha * g') * (u' + shift) with g' = min(g, limit), u' = clamp(u, -limit, limit),
 //                  one rounding on store: act [N * top, ff].  Weights [E, 2 ff, width]: an expert's gate rows, then
@@ -42,7 +44,7 @@ __device__ __forceinline__ void fma4(float& z, const float4& a, const float4& x)
 template <typename T, int TOK>
 __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, int* __restrict__ ids,
                                  float* __restrict__ weights, int n, int width, int n_experts, int top, float scale,
-                                 int renormalize, int n_extra, float* __restrict__ extra) {
+                                 int renormalize, int n_extra, float* __restrict__ extra, int softmax, float renorm_eps) {
     pdl_wait();
     extern __shared__ __align__(16) float smem[];
     float* x = smem;                                     // [TOK][width]
@@ -131,7 +133,8 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
 #pragma unroll
             for (int k = 0; k < TOK; ++k) {
                 const float zk = warp_sum(z[r][k]);
-                if (lane == 0 && e0 + r < n_rows) s[k * n_rows + e0 + r] = 1.0f / (1.0f + expf(-zk));
+                if (lane == 0 && e0 + r < n_rows)
+                    s[k * n_rows + e0 + r] = (softmax && e0 + r < n_experts) ? zk : 1.0f / (1.0f + expf(-zk));
             }
         }
     }
@@ -140,6 +143,17 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
     float* sk = s + (size_t)warp * n_rows;
     const size_t t = (size_t)t0 + warp;
     for (int e = lane; e < n_extra; e += 32) extra[t * n_extra + e] = sk[n_experts + e];
+    if (softmax) {                                       // the experts' entries hold logits: scores over all of them
+        float top_z = -INFINITY;
+        for (int e = lane; e < n_experts; e += 32) top_z = fmaxf(top_z, sk[e]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) top_z = fmaxf(top_z, __shfl_xor_sync(0xffffffffu, top_z, o));
+        float sum = 0.0f;
+        for (int e = lane; e < n_experts; e += 32) { const float p = expf(sk[e] - top_z); sk[e] = p; sum += p; }
+        sum = warp_sum(sum);
+        for (int e = lane; e < n_experts; e += 32) sk[e] = sk[e] / sum;
+        __syncwarp();
+    }
     float total = 0.0f;
     for (int c = 0; c < top; ++c) {
         // the largest score left; among equals the lowest index
@@ -162,7 +176,7 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
         __syncwarp();
     }
     if (lane == 0) {
-        const float f = renormalize ? scale / total : scale;
+        const float f = renormalize ? scale / (total + renorm_eps) : scale;
         for (int c = 0; c < top; ++c) weights[t * top + c] *= f;
     }
 }
@@ -254,7 +268,7 @@ __global__ void moe_down_kernel(const T* __restrict__ act, const T* __restrict__
 
 template <typename T, int TOK>
 int launch_route(const void* h, const float* router, int* ids, float* weights, int n, int width, int n_experts, int top, float scale,
-                 int renormalize, int n_extra, float* extra, cudaStream_t stream) {
+                 int renormalize, int n_extra, float* extra, int softmax, float renorm_eps, cudaStream_t stream) {
     const size_t smem = sizeof(float) * TOK * ((size_t)width + n_experts + n_extra);
     if (smem > 200 * 1024) return PB_ERR_TOO_LARGE;
     static size_t allowed = 48 * 1024;
@@ -267,16 +281,16 @@ int launch_route(const void* h, const float* router, int* ids, float* weights, i
     if (warps > 16) warps = 16;
     if (warps < TOK) warps = TOK;                                         // warp k picks for token k
     return launch_pdl(moe_route_kernel<T, TOK>, dim3((n + TOK - 1) / TOK), dim3(32 * warps), smem, stream, (const T*)h, router, ids,
-                      weights, n, width, n_experts, top, scale, renormalize, n_extra, extra);
+                      weights, n, width, n_experts, top, scale, renormalize, n_extra, extra, softmax, renorm_eps);
 }
 
 template <typename T>
 int dispatch_route(const void* h, const float* router, int* ids, float* weights, int n, int width, int n_experts, int top, float scale,
-                   int renormalize, int n_extra, float* extra, cudaStream_t stream) {
+                   int renormalize, int n_extra, float* extra, int softmax, float renorm_eps, cudaStream_t stream) {
     // tokens a block shares the router's rows among: one where the step is a few tokens (their blocks run side by side),
     // eight where their float32 rows leave room for three blocks on a SM, else four
     const size_t row = sizeof(float) * ((size_t)width + n_experts + n_extra);
-#define PB_ROUTE(TOK) return launch_route<T, TOK>(h, router, ids, weights, n, width, n_experts, top, scale, renormalize, n_extra, extra, stream)
+#define PB_ROUTE(TOK) return launch_route<T, TOK>(h, router, ids, weights, n, width, n_experts, top, scale, renormalize, n_extra, extra, softmax, renorm_eps, stream)
     if (n <= 16) PB_ROUTE(1);
     if (8 * row <= 72 * 1024) PB_ROUTE(8);
     PB_ROUTE(4);
@@ -287,12 +301,13 @@ int dispatch_route(const void* h, const float* router, int* ids, float* weights,
 
 // router [n_experts + n_extra, width]: the rows behind the experts' are scored too (sigmoid) and go to extra [n, n_extra].
 PB_EXPORT int pb_moe_route(int dtype, const void* h, const float* router, int* ids, float* weights, int n, int width, int n_experts,
-                           int top, float scale, int renormalize, int n_extra, float* extra, cudaStream_t stream) {
+                           int top, float scale, int renormalize, int n_extra, float* extra, int softmax, float renorm_eps,
+                           cudaStream_t stream) {
     if (n <= 0) return 0;
     if (width <= 0 || n_experts <= 0 || top <= 0 || top > n_experts || n_extra < 0 || (n_extra > 0 && extra == nullptr)) return PB_ERR_BAD_SIZE;
-    if (dtype == PB_F32) return dispatch_route<float>(h, router, ids, weights, n, width, n_experts, top, scale, renormalize, n_extra, extra, stream);
+    if (dtype == PB_F32) return dispatch_route<float>(h, router, ids, weights, n, width, n_experts, top, scale, renormalize, n_extra, extra, softmax, renorm_eps, stream);
     if (dtype == PB_BF16)
-        return dispatch_route<__nv_bfloat16>(h, router, ids, weights, n, width, n_experts, top, scale, renormalize, n_extra, extra, stream);
+        return dispatch_route<__nv_bfloat16>(h, router, ids, weights, n, width, n_experts, top, scale, renormalize, n_extra, extra, softmax, renorm_eps, stream);
     return PB_ERR_BAD_DTYPE;
 }
 

@@ -1,5 +1,5 @@
 """Model assembly.  Importing this package registers the built-in architectures."""
-from . import bubotar, megusun, qwen3, topunex  # noqa: F401
+from . import bubotar, bumotar, megusun, qwen3, topunex  # noqa: F401
 from .decoder import DecoderModel
 
 

@@ -67,9 +67,21 @@ class DecoderModel(Part):
                 needs[call.state] = own
             elif getattr(self.blocks[call.block], "state_need", lambda: None)() is not None:
                 raise ValueError(f"block {call.block} keeps state of its own: its entry of the run order must name a state entry")
+            more = tuple(getattr(mixer, "member_needs", lambda: ())())
+            if len(more) != len(call.members):
+                raise ValueError(f"block {call.block}: its mixer has {len(more)} members behind the first, the run order names "
+                                 f"{len(call.members)} cache entries for them")
+            for entry, member_need in zip(call.members, more):
+                if needs[entry] is not None:
+                    raise ValueError(f"cache entry {entry} is used twice")
+                needs[entry] = member_need
+            if call.opens is not None and (spec.walk is None or not (0 <= call.opens < spec.walk.times)):
+                raise ValueError(f"run order opens walk {call.opens}, the model's walks are {spec.walk}")
         if any(n is None for n in needs):
             raise ValueError("run order leaves a cache entry unused")
         self._needs = needs
+        self.walk_in: Optional[torch.Tensor] = None
+        self.walk_step: Optional[torch.Tensor] = None
 
     def cache_needs(self) -> List[CacheNeed]:
         return list(self._needs)
@@ -83,6 +95,9 @@ class DecoderModel(Part):
     def weight_specs(self) -> List[WeightSpec]:
         s = self.spec
         specs = [WeightSpec(s.embed_name, (s.vocab_size, s.hidden))]
+        if s.walk is not None:
+            specs += [WeightSpec(s.walk.in_name, (s.hidden, 2 * s.hidden), init="wide"),
+                      WeightSpec(s.walk.step_name, (s.walk.times, s.hidden), role="vector", init="small")]
         for b in self.blocks:
             specs += b.weight_specs()
         specs += self.final_norm.weight_specs()
@@ -95,6 +110,8 @@ class DecoderModel(Part):
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         s = self.spec
         self.embed = tensors[s.embed_name]
+        if s.walk is not None:
+            self.walk_in, self.walk_step = tensors[s.walk.in_name], tensors[s.walk.step_name].contiguous()
         for b in self.blocks:
             b.load(tensors)
         self.final_norm.load(tensors)
@@ -107,16 +124,37 @@ class DecoderModel(Part):
         it, the final norm, the head, and ``n_tokens`` rows of the embedding."""
         total = sum(self.blocks[c.block].weight_bytes() for c in self.spec.run_order)
         total += self.final_norm.weight_bytes() + self.head.numel() * self.head.element_size()
+        if self.walk_in is not None:
+            opened = sum(1 for c in self.spec.run_order if c.opens is not None)
+            total += opened * (self.walk_in.numel() * self.walk_in.element_size() + self.spec.hidden * 4)
         return total + n_tokens * self.spec.hidden * self.embed.element_size()
 
     # ---------------------------------------------------------------- one step
+    def _open_walk(self, ctx: StepContext, residual: torch.Tensor, delta: Optional[torch.Tensor], origin: torch.Tensor, t: int) -> None:
+        """x <- W [x ; x0] + step[t] on the float32 stream (x = residual + what is pending); nothing is pending afterwards.  The
+        product's operand is the two streams side by side in the activation dtype, its rows are float32."""
+        ctx.prepared_norms.clear()
+        ctx.normed.clear()
+        n, width = residual.shape
+        both = ctx.scratch("walk.in", (n, 2 * width))
+        ops.concat_streams(residual, delta, origin, both)
+        ops.linear(both, self.walk_in, residual)
+        ops.add_bias(residual, self.walk_step[t])
+        return None
+
     def forward(self, ctx: StepContext) -> torch.Tensor:
         """Logits float32 [len(ctx.logit_rows), vocab] for the tokens of ``ctx``."""
         s = self.spec
         residual = ctx.scratch("residual", (ctx.n_tokens, s.hidden), torch.float32)
         ops.embed(self.embed, ctx.token_ids, residual, s.embedding_multiplier)
+        origin = None
+        if s.walk is not None:                   # every walk's opening reads the embedding rows again
+            origin = ctx.scratch("residual.origin", (ctx.n_tokens, s.hidden), torch.float32)
+            ops.embed(self.embed, ctx.token_ids, origin, s.embedding_multiplier)
         delta = None
         for i, call in enumerate(s.run_order):
+            if call.opens is not None:
+                delta = self._open_walk(ctx, residual, delta, origin, call.opens)
             following = self.blocks[s.run_order[i + 1].block] if i + 1 < len(s.run_order) else None
             ctx.next_norm = getattr(following, "mixer_norm", None)
             ctx.next_block, ctx.next_call = following, (s.run_order[i + 1] if following is not None else None)
@@ -124,6 +162,8 @@ class DecoderModel(Part):
             view = ctx.cache(call.cache)
             if call.state is not None:
                 view.block_state = ctx.cache(call.state).state
+            if call.members:
+                view.members = [ctx.cache(entry) for entry in call.members]
             delta = self.blocks[call.block].forward(ctx, residual, delta, view)
             if ctx.moved_residual is not None:
                 residual, ctx.moved_residual = ctx.moved_residual, None

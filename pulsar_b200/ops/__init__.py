@@ -44,7 +44,7 @@ _SIGNATURES = {
     "pb_move_ids": [_P, _P, _P, _P, _I, _P],
     "pb_table_update": [_P, _I, _P, _P, _I, _I, _P, _P],
     "pb_add_rmsnorm": [_I, _P, _P, _P, _P, _P, _I, _I, _F, _I, _P],
-    "pb_rope_table": [_P, _P, _P, _P, _I, _I, _P],
+    "pb_rope_table": [_P, _P, _P, _P, _I, _I, _F, _P],
     "pb_qk_norm_rope_write": [_I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _P],
     "pb_silu_mul": [_I, _P, _P, _I, _I, _P],
     "pb_paged_attention_generic": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
@@ -105,10 +105,10 @@ _SIGNATURES = {
     "pb_clamped_glu": [_I, _P, _P, _I, _I, _F, _F, _P],
     "pb_post_norm_add_bias": [_I, _P, _P, _P, _P, _F, _P, _I, _I, _P],
     "pb_glu_bias": [_I, _I, _P, _P, _P, _I, _I, _F, _F, _F, _P],
-    "pb_qk_prepare": [_I, _I, _P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
-    "pb_sigmoid_gate_strided": [_I, _I, _P, _P, _L, _I, _I, _P],
+    "pb_qk_prepare": [_I, _I, _P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P, _F, _I, _I, _P],
+    "pb_sigmoid_gate_strided": [_I, _I, _P, _P, _L, _I, _I, _I, _P],
     "pb_add_bias": [_I, _P, _P, _I, _I, _P],
-    "pb_moe_route": [_I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P],
+    "pb_moe_route": [_I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _I, _F, _P],
     "pb_moe_gate_up": [_I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _F, _P, _P],
     "pb_moe_down": [_I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "pb_moe_grouped_workspace": [_I, _I, _I],
@@ -120,6 +120,10 @@ _SIGNATURES = {
     "pb_min_gru_run": [],
     "pb_min_gru": [_I, _P, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P],
     "pb_diff_combine": [_I, _I, _P, _P, _I, _I, _I, _I, _F, _F, _F, _P],
+    "pb_retention_chunk": [],
+    "pb_retention": [_I, _P, _L, _P, _P, _P, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
+    "pb_scaled_sum": [_I, _P, _P, _P, _F, _F, ctypes.c_longlong, _P],
+    "pb_concat_streams": [_I, _P, _P, _P, _P, _I, _I, _P],
 }
 _fns = {}
 # the entry points that launch kernels (the others answer questions on the host): what PULSAR_PROF=1 times
@@ -131,7 +135,7 @@ _LAUNCHERS = {"embed", "scale_cap", "move_ids", "add_rmsnorm", "rope_table", "qk
               "paged_attention_general", "paged_attention_general_tiled", "paged_attention_general_tc", "qkv_split_write", "heads_linear", "latent_prepare", "latent_expand_keys", "sigmoid_gate", "causal_conv_silu",
               "selective_scan", "selective_scan_prompt", "selective_scan_chunked", "post_norm_add", "clamped_glu",
               "post_norm_add_bias", "glu_bias", "qk_prepare", "sigmoid_gate_strided", "add_bias", "moe_route", "moe_gate_up", "moe_down", "moe_grouped",
-              "norm_shift", "parallel_add", "activation", "min_gru", "diff_combine"}
+              "norm_shift", "parallel_add", "activation", "min_gru", "diff_combine", "retention", "scaled_sum", "concat_streams"}
 
 
 class KernelError(RuntimeError):
@@ -237,14 +241,17 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: t
                                float(eps), int(write_back), stream()), "add_rmsnorm")
 
 
-def rope_table(positions: torch.Tensor, quadrants_per_position: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
+def rope_table(positions: torch.Tensor, quadrants_per_position: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+               magnitude: float = 1.0) -> None:
+    """cos / sin [N, half] of position * frequency (the table holds quadrants per position in float64), each multiplied by
+    ``magnitude``."""
     _cuda(positions, quadrants_per_position, cos, sin)
     half = quadrants_per_position.numel()
     assert positions.dtype == torch.int32 and quadrants_per_position.dtype == torch.float64
     assert cos.dtype == torch.float32 and sin.dtype == torch.float32
     assert cos.shape == (positions.numel(), half) and sin.shape == cos.shape
     check(fn("pb_rope_table")(_p(positions), _p(quadrants_per_position), _p(cos), _p(sin), positions.numel(), half,
-                              stream()), "rope_table")
+                              float(magnitude), stream()), "rope_table")
 
 
 def qk_norm_rope_write(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[torch.Tensor],
@@ -1242,17 +1249,27 @@ def glu_bias(gate_up: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Ten
 def qk_prepare(rows: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
                slots: Optional[torch.Tensor], cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], n_heads: int,
                n_kv_heads: int, head_dim: int, rotary: int, page_size: int, q_bias: Optional[torch.Tensor] = None,
-               k_bias: Optional[torch.Tensor] = None, unit_norm_eps: Optional[float] = None, values_from_keys: bool = False) -> None:
+               k_bias: Optional[torch.Tensor] = None, unit_norm_eps: Optional[float] = None, values_from_keys: bool = False,
+               q_norm: Optional[torch.Tensor] = None, k_norm: Optional[torch.Tensor] = None, norm_eps: Optional[float] = None,
+               n_value_heads: int = 0, value_dim: int = 0) -> None:
     """Per head of the projection rows ``rows`` [N, >= (Hq + Hkv) * D] (query heads, then key heads; float32 or the
     pools' dtype; a column slice of a wider tensor will do): + bias; a key head as it then is goes to the value pool
     (``values_from_keys``); the first ``rotary`` dimensions turn in the rotate-half layout by ``cos`` / ``sin``
     [N, rotary / 2]; the head is divided by its root mean square (``unit_norm_eps``, no weight).  Queries to float32
-    ``q_out`` [N, Hq, D], keys into their pages.  ``n_kv_heads`` 0: queries only."""
-    _cuda(q_out, k_pool, v_pool, slots, cos, sin, q_bias, k_bias)
+    ``q_out`` [N, Hq, D], keys into their pages.  ``n_kv_heads`` 0: queries only.  ``norm_eps`` with ``q_norm`` / ``k_norm``
+    (float32 [D]): a weighted RMS norm of every query and key head before the rotation.  ``n_value_heads`` value heads of
+    ``value_dim`` behind the key heads in the row go to ``v_pool`` [pages, Hv, page, Dv] as they are."""
+    _cuda(q_out, k_pool, v_pool, slots, cos, sin, q_bias, k_bias, q_norm, k_norm)
     _check_against(k_pool)
     n = rows.shape[0]
-    assert rows.is_cuda and rows.stride(1) == 1 and rows.shape[1] >= (n_heads + n_kv_heads) * head_dim
+    assert rows.is_cuda and rows.stride(1) == 1 and rows.shape[1] >= (n_heads + n_kv_heads) * head_dim + n_value_heads * value_dim
     assert q_out.dtype == torch.float32 and q_out.shape == (n, n_heads, head_dim)
+    if norm_eps is not None:
+        assert q_norm.dtype == torch.float32 and q_norm.numel() == head_dim
+        assert n_kv_heads == 0 or (k_norm.dtype == torch.float32 and k_norm.numel() == head_dim)
+    if n_value_heads:
+        assert n_kv_heads and not values_from_keys and v_pool.shape[1:] == (n_value_heads, page_size, value_dim)
+        assert v_pool.dtype == k_pool.dtype
     pool_dtype = k_pool.dtype if n_kv_heads else rows.dtype
     if n_kv_heads:
         assert slots.dtype == torch.int32 and k_pool.shape[1:] == (n_kv_heads, page_size, head_dim)
@@ -1264,16 +1281,19 @@ def qk_prepare(rows: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[torch.T
     check(fn("pb_qk_prepare")(code(rows.dtype), code(pool_dtype), _p(rows), rows.stride(0), _p(q_bias), _p(k_bias), _p(cos), _p(sin),
                               _p(q_out), _p(k_pool), _p(v_pool), _p(slots), n, n_heads, n_kv_heads, head_dim, int(rotary),
                               -1.0 if unit_norm_eps is None else float(unit_norm_eps), 1 if values_from_keys else 0, page_size,
-                              stream()), "qk_prepare")
+                              _p(q_norm), _p(k_norm) if n_kv_heads else None, -1.0 if norm_eps is None else float(norm_eps),
+                              int(n_value_heads), int(value_dim), stream()), "qk_prepare")
 
 
-def sigmoid_gate_strided(x: torch.Tensor, gate: torch.Tensor) -> None:
-    """x[n, :] *= sigmoid(gate[n, :]) in place (float32 arithmetic); ``gate`` float32 or of x's dtype, possibly a column slice."""
+def sigmoid_gate_strided(x: torch.Tensor, gate: torch.Tensor, group: int = 1) -> None:
+    """x[n, c] *= sigmoid(gate[n, c // group]) in place (float32 arithmetic); ``gate`` float32 or of x's dtype, possibly a column
+    slice.  ``group`` neighbouring columns of x share one gate column (a head's width: one gate per head)."""
     _cuda(x)
     n, width = x.shape
-    assert gate.is_cuda and gate.shape == (n, width) and gate.stride(1) == 1
-    check(fn("pb_sigmoid_gate_strided")(code(x.dtype), code(gate.dtype), _p(x), _p(gate), gate.stride(0), n, width, stream()),
-          "sigmoid_gate_strided")
+    assert group >= 1 and width % group == 0
+    assert gate.is_cuda and gate.shape == (n, width // group) and gate.stride(1) == 1
+    check(fn("pb_sigmoid_gate_strided")(code(x.dtype), code(gate.dtype), _p(x), _p(gate), gate.stride(0), n, width, int(group),
+                                        stream()), "sigmoid_gate_strided")
 
 
 def add_bias(x: torch.Tensor, bias: torch.Tensor) -> None:
@@ -1285,10 +1305,12 @@ def add_bias(x: torch.Tensor, bias: torch.Tensor) -> None:
 
 # ---------------------------------------------------------------- mixture of experts
 def moe_route(h: torch.Tensor, router: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, scale: float = 1.0,
-              renormalize: bool = False, extra: Optional[torch.Tensor] = None) -> None:
+              renormalize: bool = False, extra: Optional[torch.Tensor] = None, softmax: bool = False, renorm_eps: float = 0.0) -> None:
     """ids [N, top] int32 and weights [N, top] float32 of the ``top`` largest sigmoid(router @ h) per token (float32 sums;
     ties go to the lower index), weights times ``scale`` (after division by their sum with ``renormalize``).  With ``extra``
-    (float32 [N, X]) the router has X more rows behind the experts' that compete for nothing: their sigmoids go there."""
+    (float32 [N, X]) the router has X more rows behind the experts' that compete for nothing: their sigmoids go there.
+    ``softmax``: the scores are softmax(router @ h) over all experts instead; ``renorm_eps`` is added to the chosen scores' sum
+    before the division."""
     _cuda(h, router, ids, weights, extra)
     n, width = h.shape
     n_extra = 0 if extra is None else extra.shape[1]
@@ -1298,7 +1320,7 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, ids: torch.Tensor, weights:
     assert weights.dtype == torch.float32 and weights.shape == (n, top)
     assert extra is None or (extra.dtype == torch.float32 and extra.shape == (n, n_extra))
     check(fn("pb_moe_route")(code(h.dtype), _p(h), _p(router), _p(ids), _p(weights), n, width, e, top, float(scale),
-                             1 if renormalize else 0, n_extra, _p(extra), stream()), "moe_route")
+                             1 if renormalize else 0, n_extra, _p(extra), 1 if softmax else 0, float(renorm_eps), stream()), "moe_route")
 
 
 def moe_gate_up(h: torch.Tensor, w_gate_up: torch.Tensor, ids: torch.Tensor, act: torch.Tensor, gating,
@@ -1474,3 +1496,55 @@ def diff_combine(maps: torch.Tensor, out: torch.Tensor, n_kv_heads: int, lam: fl
     assert h2 % 2 == 0 and out.shape == (n, h2 // 2, dv) and (h2 // 2) % n_kv_heads == 0
     check(fn("pb_diff_combine")(code(maps.dtype), code(out.dtype), _p(maps), _p(out), n, h2 // 2, int(n_kv_heads), dv, float(lam),
                                 float(eps), float(gain), stream()), "diff_combine")
+
+
+# ---------------------------------------------------------------- retention
+RETENTION_CHUNKED_MIN = 32     # portions of at least this many tokens take the recurrence in chunks, parallel over chunks
+
+
+def retention(ctx, rows: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], decay: torch.Tensor,
+              state: torch.Tensor, y: torch.Tensor, n_heads: int, key_dim: int, value_dim: int, rotary: int, key_scale: float,
+              eps: float, chunked: Optional[bool] = None) -> None:
+    """Linear attention with a fixed decay per head over the step's tokens.  ``rows`` float32 [N, >= 2 H (D + V)] holds per
+    token q (H*D) | k (H*D) | v (H*V) | g (H*V); the first ``rotary`` dimensions of every q and k head turn in the rotate-half
+    layout by ``cos`` / ``sin`` [N, rotary / 2], k is then multiplied by ``key_scale``.  Per head S <- decay S + k v^T
+    (``state`` [slots, >= H*D*V] float32, each sequence's kept matrices), o = S^T q, and ``y`` [N, H*V] = o / rms(o) *
+    silu(g) with ``eps`` inside the root.  ``chunked``: None picks the form that is parallel over chunks of tokens for steps
+    with portions of ``RETENTION_CHUNKED_MIN`` tokens or more, False never, True always."""
+    _cuda(cos, sin, decay, y)
+    n = rows.shape[0]
+    H, D, V = int(n_heads), int(key_dim), int(value_dim)
+    assert rows.is_cuda and rows.dtype == torch.float32 and rows.stride(1) == 1 and rows.shape[1] >= 2 * H * (D + V)
+    assert decay.dtype == torch.float32 and decay.numel() == H and y.shape == (n, H * V)
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.shape[1] >= H * D * V and state.stride(1) == 1 and state.is_cuda
+    if rotary:
+        assert cos.dtype == torch.float32 and cos.shape == (n, rotary // 2) and sin.shape == cos.shape and sin.dtype == cos.dtype
+    qr = ctx.scratch("retention.q", (n, H, D), torch.float32)
+    kr = ctx.scratch("retention.k", (n, H, D), torch.float32)
+    if chunked is None:
+        chunked = ctx.max_q_len >= RETENTION_CHUNKED_MIN
+    max_chunks, work, kernels = 0, None, 2
+    if chunked:
+        size = fn("pb_retention_chunk")()
+        max_chunks = sum(-(-int(q) // size) for q in ctx.host.q_lens)
+        work = ctx.scratch("retention.chunks", (max_chunks, H, D, V), torch.float32)
+        kernels = 4
+    check(fn("pb_retention")(code(y.dtype), _p(rows), rows.stride(0), _p(cos), _p(sin), _p(qr), _p(kr), _p(decay), _p(state),
+                             state.stride(0), _p(ctx.cu_q), _p(ctx.state_slots), _p(y), n, ctx.n_seqs, H, D, V, int(rotary),
+                             float(key_scale), float(eps), max_chunks, _p(work), stream()), "retention", kernels=kernels)
+
+
+def scaled_sum(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor, a: float, b: float) -> None:
+    """out = a * x + b * y element by element (float32 arithmetic, one rounding); ``out`` may be ``x`` or ``y``."""
+    _cuda(x, y, out)
+    assert x.shape == y.shape == out.shape and x.dtype == y.dtype == out.dtype
+    check(fn("pb_scaled_sum")(code(x.dtype), _p(x), _p(y), _p(out), float(a), float(b), x.numel(), stream()), "scaled_sum")
+
+
+def concat_streams(residual: torch.Tensor, delta: Optional[torch.Tensor], origin: torch.Tensor, out: torch.Tensor) -> None:
+    """out [N, 2 width] = [residual (+ delta) | origin] in ``out``'s dtype; ``residual`` and ``origin`` float32 [N, width]."""
+    _cuda(residual, delta, origin, out)
+    n, width = residual.shape
+    assert residual.dtype == origin.dtype == torch.float32 and origin.shape == (n, width) and out.shape == (n, 2 * width)
+    assert delta is None or (delta.shape == (n, width) and delta.dtype == out.dtype)
+    check(fn("pb_concat_streams")(code(out.dtype), _p(residual), _p(delta), _p(origin), _p(out), n, width, stream()), "concat_streams")

@@ -35,7 +35,10 @@ class Attention(Mixer):
     a cap on the scaled scores, first keys that stay visible below a window (``keep_first``), a learned sink per head in
     the softmax's denominator, and a sigmoid gate on the concatenated heads from a projection of the mixer's input.
     With any of these the fused projection (rows q | k | v | gate) is a float32 product, the bias is added in float32,
-    and ``ops.qk_prepare`` does what stands between it and the attention kernels.
+    and ``ops.qk_prepare`` does what stands between it and the attention kernels.  In that form the per-head norm may
+    also be the weighted one in front of the rotation (``qk_norm_weight``, not ``qk_norm_after_rotation``), the mixer may
+    have a v projection of its own (value heads of ``value_dim``), and the sink may be one given number for all heads
+    (``fixed_sink``; 0 adds one to the softmax's denominator).
 
     The differential form (``spec.differential`` = d, part of the general form without rotation, biases or per-head norm):
     every head has two score maps over the same values.  Its query rows hold [map 1 | map 2] (``head_dim`` each) and so do
@@ -61,7 +64,8 @@ class Attention(Mixer):
                              or spec.output_gate)
         self.maps = 2 if spec.differential is not None else 1          # score maps per head
         self.general = bool(spec.value_dim != spec.head_dim or spec.chunk is not None or spec.distance_bias is not None
-                            or spec.keep_first or spec.softcap is not None or spec.sinks or spec.output_gate or self.prepared
+                            or spec.keep_first or spec.softcap is not None or spec.sinks or spec.fixed_sink is not None
+                            or spec.output_gate or self.prepared
                             or self.maps > 1 or spec.q_temperature is not None)
         if (self.maps > 1 or spec.q_temperature is not None) and (self.prepared or not spec.own_kv):
             raise ValueError("attention: the differential form and the query temperature go with plain projections of its own keys")
@@ -71,10 +75,10 @@ class Attention(Mixer):
             if not self.prepared and (spec.position is not None or spec.qk_norm_eps is not None):
                 raise ValueError("attention: the general form (value width, chunk mask, distance bias) has neither rotation nor q/k norm")
             if self.prepared:
-                if spec.qk_norm_eps is not None and (spec.qk_norm_weight or not spec.qk_norm_after_rotation):
-                    raise ValueError("attention: with biases or values from keys the q/k norm is the one without a weight, behind the rotation")
-                if spec.own_kv and not spec.values_from_keys:
-                    raise ValueError("attention: biases and the weightless q/k norm are implemented for values that are the keys")
+                if spec.qk_norm_eps is not None and spec.qk_norm_weight == spec.qk_norm_after_rotation:
+                    raise ValueError("attention: the q/k norm is the weighted one before the rotation or the one without a weight behind it")
+                if spec.sinks and spec.fixed_sink is not None:
+                    raise ValueError("attention: a sink is learned per head or one given number, not both")
                 if spec.values_from_keys and spec.value_dim != spec.head_dim:
                     raise ValueError("attention: values that are the keys are as wide as the keys")
             if spec.head_dim <= 0 or spec.value_dim <= 0 or (spec.chunk is not None and spec.chunk <= 0):
@@ -153,6 +157,8 @@ class Attention(Mixer):
             self.output_bias = tensors[p + nm["o_bias"]]
         if s.sinks:
             self.sinks = tensors[p + nm["sinks"]]
+        elif s.fixed_sink is not None:
+            self.sinks = torch.full((s.n_heads,), float(s.fixed_sink), dtype=torch.float32, device=self.w_o.device)
         if s.qk_norm_eps is not None and s.qk_norm_weight:
             self.q_norm = tensors[p + nm["q_norm"]]
             self.k_norm = tensors.get(p + nm["k_norm"])
@@ -205,9 +211,13 @@ class Attention(Mixer):
             if self.position is not None:
                 cos, sin = self.position.tables(ctx)
                 rotary = s.position.rotary_dim
+            weighted = s.qk_norm_eps is not None and s.qk_norm_weight          # in front of the rotation, with a weight
             ops.qk_prepare(qkv, q, cache.k_pool if n_kv else None, cache.v_pool if n_kv else None, cache.slots if n_kv else None,
                            cos, sin, s.n_heads, n_kv, s.head_dim, rotary, cache.page_size, self.q_bias, self.k_bias if n_kv else None,
-                           s.qk_norm_eps, s.values_from_keys)
+                           None if weighted else s.qk_norm_eps, s.values_from_keys,
+                           q_norm=self.q_norm if weighted else None, k_norm=self.k_norm if weighted else None,
+                           norm_eps=s.qk_norm_eps if weighted else None,
+                           n_value_heads=n_kv if self.own_v else 0, value_dim=s.value_dim if self.own_v else 0)
         else:
             ops.qkv_split_write(qkv, q, cache.k_pool if n_kv else None, cache.v_pool if n_kv else None,
                                 cache.slots if n_kv else None, s.n_heads * maps, n_kv * maps, s.head_dim, s.value_dim, cache.page_size,

@@ -42,6 +42,7 @@ class CacheView:
     state: Optional[torch.Tensor] = None         # [max_requests, *state_shape]
     group: int = -1
     block_state: Optional[torch.Tensor] = None   # [max_requests, *shape]: the state the block itself keeps (``Block.state_need``)
+    members: Optional[List["CacheView"]] = None  # a composite mixer: the views of its members behind the first (``LayerCall.members``)
 
     @property
     def k_pool(self) -> Optional[torch.Tensor]:

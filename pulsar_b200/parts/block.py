@@ -18,16 +18,21 @@ from .norm import RMSNorm
 class PreNormBlock(Block):
     """x += mixer(norm(x)); x += feed_forward(norm(x))
     (pulsar-core/src/model/qwen3.cpp:77-121).  The additions happen inside the norm
-    kernels, in float32, on the float32 residual stream."""
+    kernels, in float32, on the float32 residual stream.  A block without a feed-forward has
+    the first sublayer only and leaves the mixer's contribution pending."""
 
     def __init__(self, spec: BlockSpec, dtype: torch.dtype):
         self.spec = spec
         self.mixer_norm = NORMS.get(spec.mixer_norm.kind)(spec.mixer_norm, spec.sub_prefix("mixer_norm"), dtype, "norm.mixer")
         self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, spec.sub_prefix("mixer"), dtype)
-        self.feed_forward_norm = NORMS.get(spec.feed_forward_norm.kind)(
-            spec.feed_forward_norm, spec.sub_prefix("feed_forward_norm"), dtype, "norm.ffn")
-        self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, spec.sub_prefix("feed_forward"), dtype)
-        self.parts = (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+        self.feed_forward_norm = self.feed_forward = None
+        if spec.feed_forward is not None:
+            if spec.feed_forward_norm is None:
+                raise ValueError("a prenorm block with a feed-forward needs the norm before it")
+            self.feed_forward_norm = NORMS.get(spec.feed_forward_norm.kind)(
+                spec.feed_forward_norm, spec.sub_prefix("feed_forward_norm"), dtype, "norm.ffn")
+            self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, spec.sub_prefix("feed_forward"), dtype)
+        self.parts = tuple(p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward) if p is not None)
 
     def weight_specs(self) -> List[WeightSpec]:
         return [w for p in self.parts for w in p.weight_specs()]
@@ -43,10 +48,13 @@ class PreNormBlock(Block):
                 cache: CacheView) -> Optional[torch.Tensor]:
         # With nothing pending, a part may take the norm before it and the addition behind it into its own products
         # (steps of a few tokens); otherwise the norm kernel adds what is pending and normalises.
-        if delta is not None or not self.mixer.forward_normed(ctx, residual, self.mixer_norm, cache, self.feed_forward_norm):
+        after_mixer = self.feed_forward_norm if self.feed_forward is not None else ctx.next_norm
+        if delta is not None or not self.mixer.forward_normed(ctx, residual, self.mixer_norm, cache, after_mixer):
             ctx.prepared_norms.clear()
             h = self.mixer_norm.forward(ctx, residual, delta)
             delta = self.mixer.forward(ctx, h, cache)
+        if self.feed_forward is None:
+            return delta
         if delta is None and self.feed_forward.forward_normed(ctx, residual, self.feed_forward_norm, ctx.next_norm):
             return None
         ctx.prepared_norms.clear()

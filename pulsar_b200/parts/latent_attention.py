@@ -31,7 +31,9 @@ class LatentAttention(Mixer):
     keys are all among its own tokens, expands them instead (see ``forward``); the two forms compute the same function.
 
     Options (``spec.extra``): ``kv_rank``, ``rot_dim``, ``latent_norm_eps``, ``gated`` (the concatenated heads are
-    multiplied by sigmoid(W_g h), h the mixer's input).  ``spec.position`` gives the rotation (its table's
+    multiplied by sigmoid(W_g h), h the mixer's input), ``head_gate`` (the same with one gate per head: W_g has a row per
+    head and a head's whole output is multiplied by its sigmoid).  ``spec.sinks``: a learned number per head whose
+    exponential joins the softmax's denominator (tensor role "sinks").  ``spec.position`` gives the rotation (its table's
     ``rotary_dim`` leading dimensions of the rotated part turn, in neighbouring pairs).  With ``own_kv`` False the
     mixer has no down projection and attends over the rows another layer cached this step, with its own expansions.
     """
@@ -41,6 +43,9 @@ class LatentAttention(Mixer):
         self.rot_dim = int(spec.option("rot_dim", 0))
         self.norm_eps = float(spec.option("latent_norm_eps", 1e-6))
         self.gated = bool(spec.option("gated", False))
+        self.head_gate = bool(spec.option("head_gate", False))
+        if self.gated and self.head_gate:
+            raise ValueError("latent attention: the gate is one per element or one per head, not both")
         if spec.n_heads <= 0 or spec.head_dim <= 0 or spec.value_dim <= 0 or self.rank <= 0 or self.rot_dim < 0:
             raise ValueError("latent attention: heads, head sizes and the latent's rank must be positive")
         if self.rot_dim and spec.position is None:
@@ -53,7 +58,8 @@ class LatentAttention(Mixer):
         self.names = {r: name(r, d) for r, d in (("q", "q_proj.weight"), ("down", "kv_down_proj.weight"),
                                                  ("latent_norm", "kv_norm.weight"), ("up_k", "k_up_proj.weight"),
                                                  ("up_v", "v_up_proj.weight"), ("gate", "gate_proj.weight"),
-                                                 ("o", "o_proj.weight"))}
+                                                 ("o", "o_proj.weight"), ("sinks", "sinks"))}
+        self.sinks = None
         self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.latent_norm = self.w_uk_rows = self.w_uv_rows = None
 
     @property
@@ -69,9 +75,11 @@ class LatentAttention(Mixer):
                       WeightSpec(p + nm["latent_norm"], (self.rank,), role="vector", init="ones_normal")]
         specs += [WeightSpec(p + nm["up_k"], (s.n_heads * s.head_dim, self.rank)),
                   WeightSpec(p + nm["up_v"], (s.n_heads * s.value_dim, self.rank))]
-        if self.gated:
-            specs.append(WeightSpec(p + nm["gate"], (s.n_heads * s.value_dim, s.hidden)))
+        if self.gated or self.head_gate:
+            specs.append(WeightSpec(p + nm["gate"], (s.n_heads * (s.value_dim if self.gated else 1), s.hidden)))
         specs.append(WeightSpec(p + nm["o"], (s.hidden, s.n_heads * s.value_dim)))
+        if s.sinks:
+            specs.append(WeightSpec(p + nm["sinks"], (s.n_heads,), role="vector", init="small"))
         return specs
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -80,8 +88,10 @@ class LatentAttention(Mixer):
         if s.own_kv:
             rows.append(tensors[p + nm["down"]])
             self.latent_norm = tensors[p + nm["latent_norm"]]
-        if self.gated:
+        if self.gated or self.head_gate:
             rows.append(tensors[p + nm["gate"]])
+        if s.sinks:
+            self.sinks = tensors[p + nm["sinks"]]
         self.w_in = torch.cat(rows, dim=0).contiguous() if len(rows) > 1 else rows[0]      # rows: q | down | gate
         # per head [inputs, outputs]: the key expansion as stored serves the query side (head_dim -> rank), the value
         # expansion is transposed once (rank -> value_dim)
@@ -91,7 +101,7 @@ class LatentAttention(Mixer):
         self.w_o = tensors[p + nm["o"]]
 
     def weight_bytes(self) -> int:
-        ts = [self.w_in, self.w_uk_t, self.w_uv, self.w_o, self.latent_norm]      # a step reads one form of the expansions
+        ts = [self.w_in, self.w_uk_t, self.w_uv, self.w_o, self.latent_norm, self.sinks]      # a step reads one form of the expansions
         return sum(t.numel() * t.element_size() for t in ts if t is not None)
 
     def cache_need(self) -> CacheNeed:
@@ -106,6 +116,7 @@ class LatentAttention(Mixer):
         q = proj[:, :q_width]
         down = proj[:, q_width:q_width + self.row] if s.own_kv else None
         gate = proj[:, self.w_in.shape[0] - H * s.value_dim:] if self.gated else None
+        head_gate = proj[:, self.w_in.shape[0] - H:] if self.head_gate else None
         if self.position is not None:
             cos, sin = self.position.tables(ctx)
         else:
@@ -121,6 +132,8 @@ class LatentAttention(Mixer):
                 ops.sigmoid_gate(heads.view(n, H * s.value_dim), gate)
         else:
             heads = self._absorbed(ctx, q, down, gate, cos, sin, cache)
+        if head_gate is not None:
+            ops.sigmoid_gate_strided(heads.view(n, H * s.value_dim), head_gate, group=s.value_dim)
         out = ctx.scratch("latent.out", (n, s.hidden))
         ops.linear(heads.view(n, H * s.value_dim), self.w_o, out)
         return out
@@ -134,7 +147,7 @@ class LatentAttention(Mixer):
                            pool if s.own_kv else None, q_full, H, s.head_dim, self.rot_dim, self.rank, cache.page_size)
         mixed = ctx.scratch("latent.mixed", (n, H, self.rank))
         ops.paged_attention_general(ctx, q_full, pool, pool, mixed, cache.block_table, s.scale, s.window, s.chunk, None,
-                                    key_width=self.row, value_width=self.rank)
+                                    key_width=self.row, value_width=self.rank, sinks=self.sinks)
         heads = ctx.scratch("latent.heads", (n, H, s.value_dim))
         ops.heads_linear(mixed, self.w_uv, heads, gate)
         return heads
@@ -167,5 +180,5 @@ class LatentAttention(Mixer):
             ctx.shared["rows_as_pages"] = table
         heads = ctx.scratch("latent.heads", (n, H, s.value_dim))
         ops.paged_attention_general(ctx, q_cat, keys.view(n, H, 1, s.head_dim + self.rot_dim), values.view(n, H, 1, s.value_dim),
-                                    heads, table, s.scale, None, s.chunk, None)
+                                    heads, table, s.scale, None, s.chunk, None, sinks=self.sinks)
         return heads

@@ -25,7 +25,10 @@ class MixtureOfExperts(FeedForward):
     takes each once.  With ``shared_gate`` (a tensor name behind the prefix, [1, width]) the shared expert's output is
     multiplied by sigmoid(<that row, h>), one number per token; the row rides in the router's product as one more row.
 
-    Options (``spec.extra``): ``experts``, ``top``, ``router_scale``, ``renormalize``, ``limit``, ``alpha``, ``shift``,
+    With ``scoring`` "softmax" the scores are s = softmax(W_r h) over all experts instead of sigmoids, and ``renorm_eps`` is added
+    to the chosen scores' sum before a renormalising division.
+
+    Options (``spec.extra``): ``experts``, ``top``, ``router_scale``, ``renormalize``, ``scoring``, ``renorm_eps``, ``limit``, ``alpha``, ``shift``,
     ``weight_input``, ``shared`` (FeedForwardSpec or None), ``shared_prefix`` ("shared."), ``shared_gate``, ``tensor_names``
     by role "router", "gate", "up", "down" (an expert's tensors are ``<prefix>e<i>.<name>``).
 
@@ -42,6 +45,10 @@ class MixtureOfExperts(FeedForward):
             raise ValueError(f"moe: top ({self.top}) must lie between 1 and the number of experts ({self.n_experts})")
         self.router_scale = float(spec.option("router_scale", 1.0))
         self.renormalize = bool(spec.option("renormalize", False))
+        self.scoring = str(spec.option("scoring", "sigmoid"))
+        if self.scoring not in ("sigmoid", "softmax"):
+            raise ValueError(f"moe: scoring '{self.scoring}' is not one of sigmoid, softmax")
+        self.renorm_eps = float(spec.option("renorm_eps", 0.0))
         limit = spec.option("limit", None)
         self.gating = (float(limit) if limit else 0.0, float(spec.option("alpha", 1.702)), float(spec.option("shift", 1.0)))
         names = dict(spec.option("tensor_names", ()))
@@ -94,7 +101,8 @@ class MixtureOfExperts(FeedForward):
         ids = ctx.scratch("moe.ids", (n, top), torch.int32)
         weights = ctx.scratch("moe.weights", (n, top), torch.float32)
         shared_scale = ctx.scratch("moe.shared_scale", (n, 1), torch.float32) if self.shared_gate_name is not None else None
-        ops.moe_route(h, self.router, ids, weights, self.router_scale, self.renormalize, shared_scale)
+        ops.moe_route(h, self.router, ids, weights, self.router_scale, self.renormalize, shared_scale,
+                      softmax=self.scoring == "softmax", renorm_eps=self.renorm_eps)
         shared = self.shared.forward(ctx, h) if self.shared is not None else None
         act = ctx.scratch("moe.act", (n * top, s.intermediate))
         out = ctx.scratch("moe.out", (n, s.hidden))
