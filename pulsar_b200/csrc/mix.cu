@@ -1,7 +1,7 @@
 // Small kernels around composite mixers and repeated walks over a run of layers.
 //
 //   scaled_sum       out[i] = a * x[i] + b * y[i] (float32 arithmetic, one rounding on store): two mixers side by side whose
-//                    outputs join with a weight each.
+//                    outputs join with a weight each.  x and y are of one dtype, out of its own.
 //   concat_streams   out[n] = [ residual[n] (+ delta[n]) | origin[n] ] in the activation dtype: the operand of the product that
 //                    opens a walk, x <- W [x ; x0].  residual and origin are float32 [N, width]; delta (optional) is what the
 //                    layer before left pending.
@@ -11,8 +11,8 @@ namespace {
 
 using namespace pb;
 
-template <typename T>
-__global__ void scaled_sum_kernel(const T* __restrict__ x, const T* __restrict__ y, T* __restrict__ out, float a, float b, size_t total) {
+template <typename TIn, typename T>
+__global__ void scaled_sum_kernel(const TIn* __restrict__ x, const TIn* __restrict__ y, T* __restrict__ out, float a, float b, size_t total) {
     pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
         out[i] = from_float<T>(fmaf(a, to_float(x[i]), b * to_float(y[i])));
@@ -37,14 +37,16 @@ unsigned blocks_for(size_t total) {
 
 }  // namespace
 
-PB_EXPORT int pb_scaled_sum(int dtype, const void* x, const void* y, void* out, float a, float b, long long total, cudaStream_t stream) {
+PB_EXPORT int pb_scaled_sum(int in_dtype, int dtype, const void* x, const void* y, void* out, float a, float b, long long total,
+                            cudaStream_t stream) {
     if (total <= 0) return 0;
-    if (dtype == PB_F32)
-        return launch_pdl(scaled_sum_kernel<float>, dim3(blocks_for(total)), dim3(256), 0, stream, (const float*)x, (const float*)y,
-                          (float*)out, a, b, (size_t)total);
-    if (dtype == PB_BF16)
-        return launch_pdl(scaled_sum_kernel<__nv_bfloat16>, dim3(blocks_for(total)), dim3(256), 0, stream, (const __nv_bfloat16*)x,
-                          (const __nv_bfloat16*)y, (__nv_bfloat16*)out, a, b, (size_t)total);
+#define PB_SUM(TI, T) return launch_pdl(scaled_sum_kernel<TI, T>, dim3(blocks_for(total)), dim3(256), 0, stream, (const TI*)x, \
+                                        (const TI*)y, (T*)out, a, b, (size_t)total)
+    if (in_dtype == PB_F32 && dtype == PB_F32) PB_SUM(float, float);
+    if (in_dtype == PB_F32 && dtype == PB_BF16) PB_SUM(float, __nv_bfloat16);
+    if (in_dtype == PB_BF16 && dtype == PB_BF16) PB_SUM(__nv_bfloat16, __nv_bfloat16);
+    if (in_dtype == PB_BF16 && dtype == PB_F32) PB_SUM(__nv_bfloat16, float);
+#undef PB_SUM
     return PB_ERR_BAD_DTYPE;
 }
 

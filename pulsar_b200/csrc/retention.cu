@@ -47,8 +47,8 @@ __global__ void retention_prepare_kernel(const float* __restrict__ rows, long st
     for (int i = rotary + lane; i < D; i += 32) dst[i] = src[i] * f;
 }
 
-template <typename T, int PER>
-__global__ void retention_step_kernel(const float* __restrict__ qr, const float* __restrict__ kr, const float* __restrict__ rows,
+template <typename T, int PER, int THREADS>
+__global__ void __launch_bounds__(THREADS) retention_step_kernel(const float* __restrict__ qr, const float* __restrict__ kr, const float* __restrict__ rows,
                                       long stride, int v_off, int g_off, const float* __restrict__ decay, float* __restrict__ state,
                                       long state_stride, const int* __restrict__ cu_q, const int* __restrict__ state_slots,
                                       T* __restrict__ y, int H, int D, int V, int DS, float eps) {
@@ -291,16 +291,17 @@ int allow_smem(K kernel, size_t smem) {
     return (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
 }
 
-template <typename T, int PER>
+template <typename T, int PER, int THREADS>
 int launch_step(const float* qr, const float* kr, const float* rows, long stride, int v_off, int g_off, const float* decay,
                 float* state, long state_stride, const int* cu_q, const int* state_slots, void* y, int n_seqs, int H, int D, int V,
                 float eps, cudaStream_t stream) {
     const int DS = (D + PER - 1) / PER;
     const int threads = (V * DS + 31) / 32 * 32;
     const size_t smem = sizeof(float) * (2 * (size_t)D + (size_t)DS * V + 32);
-    const int rc = allow_smem(retention_step_kernel<T, PER>, smem);
+    if (threads > THREADS) return PB_ERR_TOO_LARGE;
+    const int rc = allow_smem(retention_step_kernel<T, PER, THREADS>, smem);
     if (rc != 0) return rc;
-    return launch_pdl(retention_step_kernel<T, PER>, dim3(H, n_seqs), dim3(threads), smem, stream, qr, kr, rows, stride, v_off, g_off,
+    return launch_pdl(retention_step_kernel<T, PER, THREADS>, dim3(H, n_seqs), dim3(threads), smem, stream, qr, kr, rows, stride, v_off, g_off,
                       decay, state, state_stride, cu_q, state_slots, (T*)y, H, D, V, DS, eps);
 }
 
@@ -308,20 +309,27 @@ template <typename T>
 int dispatch_step(const float* qr, const float* kr, const float* rows, long stride, int v_off, int g_off, const float* decay,
                   float* state, long state_stride, const int* cu_q, const int* state_slots, void* y, int n_seqs, int H, int D, int V,
                   float eps, cudaStream_t stream) {
-    // the fewest rows of a column per thread that keep the block within 512 threads (1024 at the largest)
-#define PB_STEP(PER) return launch_step<T, PER>(qr, kr, rows, stride, v_off, g_off, decay, state, state_stride, cu_q, state_slots, y, \
-                                               n_seqs, H, D, V, eps, stream)
-    if (V * ((D + 7) / 8) <= 512) PB_STEP(8);
-    if (V * ((D + 15) / 16) <= 512) PB_STEP(16);
-    if (V * ((D + 31) / 32) <= 512) PB_STEP(32);
-    if (V * ((D + 63) / 64) <= 1024) PB_STEP(64);
+    // the fewest rows of a column per thread that keep the block within 512 threads (256 where a thread holds 64 rows: the
+    // registers of a block are 64 K)
+#define PB_STEP(PER, THREADS) return launch_step<T, PER, THREADS>(qr, kr, rows, stride, v_off, g_off, decay, state, state_stride, cu_q, \
+                                                                 state_slots, y, n_seqs, H, D, V, eps, stream)
+    if (V * ((D + 7) / 8) <= 512) PB_STEP(8, 512);
+    if (V * ((D + 15) / 16) <= 512) PB_STEP(16, 512);
+    if (V * ((D + 31) / 32) <= 512) PB_STEP(32, 512);
+    if (V * ((D + 63) / 64) <= 256) PB_STEP(64, 256);
 #undef PB_STEP
     return PB_ERR_TOO_LARGE;
 }
 
+bool step_fits(int D, int V) { return V * ((D + 31) / 32) <= 512 || V * ((D + 63) / 64) <= 256; }
+
 }  // namespace
 
 PB_EXPORT int pb_retention_chunk() { return kChunk; }
+
+// Whether the token-by-token kernel holds a head's state of these sizes in one block's registers; where it does not, every
+// step takes the form in chunks (a single token is a chunk of one).
+PB_EXPORT int pb_retention_step_supported(int D, int V) { return D > 0 && V > 0 && step_fits(D, V) ? 1 : 0; }
 
 // rows float32 [n, stride]: q (H*D) | k (H*D) | v (H*V) | g (H*V); cos/sin float32 [n, rotary/2]; qr, kr float32 [n, H, D]
 // (workspace); decay float32 [H]; state: float32 rows of state_stride elements per slot, the first H*D*V are this mixer's
@@ -343,6 +351,7 @@ PB_EXPORT int pb_retention(int dtype, const float* rows, long stride, const floa
                         sin_t, qr, kr, H, D, rotary, k_scale);
     if (rc != 0) return rc;
     if (max_chunks <= 0) {
+        if (!step_fits(D, V)) return PB_ERR_TOO_LARGE;
         if (dtype == PB_F32)
             return dispatch_step<float>(qr, kr, rows, stride, v_off, g_off, decay, state, state_stride, cu_q, state_slots, y, n_seqs, H, D,
                                         V, eps, stream);

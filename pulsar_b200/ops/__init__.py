@@ -121,8 +121,9 @@ _SIGNATURES = {
     "pb_min_gru": [_I, _P, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P],
     "pb_diff_combine": [_I, _I, _P, _P, _I, _I, _I, _I, _F, _F, _F, _P],
     "pb_retention_chunk": [],
+    "pb_retention_step_supported": [_I, _I],
     "pb_retention": [_I, _P, _L, _P, _P, _P, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
-    "pb_scaled_sum": [_I, _P, _P, _P, _F, _F, ctypes.c_longlong, _P],
+    "pb_scaled_sum": [_I, _I, _P, _P, _P, _F, _F, ctypes.c_longlong, _P],
     "pb_concat_streams": [_I, _P, _P, _P, _P, _I, _I, _P],
 }
 _fns = {}
@@ -1522,7 +1523,8 @@ def retention(ctx, rows: torch.Tensor, cos: Optional[torch.Tensor], sin: Optiona
     qr = ctx.scratch("retention.q", (n, H, D), torch.float32)
     kr = ctx.scratch("retention.k", (n, H, D), torch.float32)
     if chunked is None:
-        chunked = ctx.max_q_len >= RETENTION_CHUNKED_MIN
+        # sizes whose state does not fit one block's registers always take the chunks (a function of the sizes alone)
+        chunked = ctx.max_q_len >= RETENTION_CHUNKED_MIN or not fn("pb_retention_step_supported")(D, V)
     max_chunks, work, kernels = 0, None, 2
     if chunked:
         size = fn("pb_retention_chunk")()
@@ -1535,10 +1537,12 @@ def retention(ctx, rows: torch.Tensor, cos: Optional[torch.Tensor], sin: Optiona
 
 
 def scaled_sum(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor, a: float, b: float) -> None:
-    """out = a * x + b * y element by element (float32 arithmetic, one rounding); ``out`` may be ``x`` or ``y``."""
+    """out = a * x + b * y element by element (float32 arithmetic, one rounding); ``x`` and ``y`` share a dtype, ``out`` has
+    its own and may be ``x`` or ``y`` where the dtypes agree."""
     _cuda(x, y, out)
-    assert x.shape == y.shape == out.shape and x.dtype == y.dtype == out.dtype
-    check(fn("pb_scaled_sum")(code(x.dtype), _p(x), _p(y), _p(out), float(a), float(b), x.numel(), stream()), "scaled_sum")
+    assert x.shape == y.shape == out.shape and x.dtype == y.dtype
+    check(fn("pb_scaled_sum")(code(x.dtype), code(out.dtype), _p(x), _p(y), _p(out), float(a), float(b), x.numel(), stream()),
+          "scaled_sum")
 
 
 def concat_streams(residual: torch.Tensor, delta: Optional[torch.Tensor], origin: torch.Tensor, out: torch.Tensor) -> None:

@@ -192,7 +192,7 @@ class Attention(Mixer):
         if s.output_gate:
             at = self.w_qkv.shape[0] - s.n_heads * s.value_dim
             ops.sigmoid_gate_strided(o.view(n, s.n_heads * s.value_dim), qkv[:, at:])
-        out = ctx.scratch("attn.out", (n, s.hidden))
+        out = ctx.scratch("attn.out", (n, s.hidden), torch.float32 if self.output_float32 else None)
         ops.linear(o.view(n, s.n_heads * s.value_dim), self.w_o, out)
         if self.output_bias is not None and not self.defer_output_bias:
             ops.add_bias(out, self.output_bias)

@@ -146,7 +146,12 @@ class PositionEncoding:
 
 
 class Mixer(Part):
-    """forward(ctx, h [N, hidden], cache: CacheView) -> delta [N, hidden]."""
+    """forward(ctx, h [N, hidden], cache: CacheView) -> delta [N, hidden].
+
+    ``output_float32``: a mixer that honours it returns float32 rows instead of rows in the activation dtype; whoever sets
+    it (a composite that weighs and adds its members' outputs) does the one rounding itself."""
+
+    output_float32: bool = False
 
     def cache_need(self) -> CacheNeed:
         return CacheNeed.none()

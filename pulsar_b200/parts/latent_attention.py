@@ -134,7 +134,7 @@ class LatentAttention(Mixer):
             heads = self._absorbed(ctx, q, down, gate, cos, sin, cache)
         if head_gate is not None:
             ops.sigmoid_gate_strided(heads.view(n, H * s.value_dim), head_gate, group=s.value_dim)
-        out = ctx.scratch("latent.out", (n, s.hidden))
+        out = ctx.scratch("latent.out", (n, s.hidden), torch.float32 if self.output_float32 else None)
         ops.linear(heads.view(n, H * s.value_dim), self.w_o, out)
         return out
 

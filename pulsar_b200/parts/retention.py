@@ -79,6 +79,6 @@ class Retention(Mixer):
         y = ctx.scratch("retention.y", (n, s.n_heads * s.value_dim))
         ops.retention(ctx, rows, cos, sin, self.decay, cache.state, y, s.n_heads, s.head_dim, s.value_dim, rotary, self.key_scale,
                       s.norm_eps)
-        out = ctx.scratch("retention.out", (n, s.hidden))
+        out = ctx.scratch("retention.out", (n, s.hidden), torch.float32 if self.output_float32 else None)
         ops.linear(y, self.w_o, out)
         return out

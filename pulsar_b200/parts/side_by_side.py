@@ -17,7 +17,8 @@ class SideBySide(Mixer):
     """out = sum over the members of scale_i * member_i(h).  A member is any registered mixer with a specification of its
     own; member i's tensors stand under ``<prefix><member prefix i>``.  Each member keeps its own cache entry: the first
     one's is the layer call's ``cache``, the others' are the call's ``members`` in order (``member_needs``), and reach
-    ``forward`` as ``cache.members``.
+    ``forward`` as ``cache.members``.  Members that can (``Mixer.output_float32``) hand over float32 rows, so that the weighted
+    sum is rounded once.
 
     Options (``spec.extra``): ``members`` (a tuple of (member prefix, MixerSpec, scale))."""
 
@@ -32,6 +33,7 @@ class SideBySide(Mixer):
             if sub_spec.hidden != spec.hidden:
                 raise ValueError("side_by_side: a member reads and writes the width of the whole")
             self.members.append(MIXERS.get(sub_spec.kind)(sub_spec, prefix + sub_prefix, dtype))
+            self.members[-1].output_float32 = True
             self.scales.append(float(scale))
 
     @property
@@ -60,12 +62,25 @@ class SideBySide(Mixer):
         if len(views) != len(self.members):
             raise ValueError(f"side_by_side: {len(self.members)} members but {len(views)} cache entries (LayerCall.members)")
         total = ctx.scratch("side.sum", (ctx.n_tokens, self.spec.hidden))
+        if len(self.members) == 2 and type(self.members[0]) is not type(self.members[1]):
+            # two parts of different kinds keep their outputs in buffers of their own: one kernel weighs and adds them
+            first = self.members[0].forward(ctx, h, views[0])
+            second = self.members[1].forward(ctx, h, views[1])
+            if first.dtype == second.dtype:
+                ops.scaled_sum(first, second, total, self.scales[0], self.scales[1])
+                return total
+            outputs = iter((first, second))
+        else:
+            outputs = None
+        # members of one kind write to the same scratch buffer, and members may hand over rows of different dtypes: each
+        # output is weighed into float32 rows and added to the running sum before the next member runs
+        shape = (ctx.n_tokens, self.spec.hidden)
+        running, part = ctx.scratch("side.running", shape, torch.float32), ctx.scratch("side.part", shape, torch.float32)
         for i, (member, view, scale) in enumerate(zip(self.members, views, self.scales)):
-            out = member.forward(ctx, h, view)
+            out = next(outputs) if outputs is not None else member.forward(ctx, h, view)
             if i == 0:
-                first, first_scale = out, scale
-            elif i == 1:
-                ops.scaled_sum(first, out, total, first_scale, scale)
+                ops.scaled_sum(out, out, running, scale, 0.0)
             else:
-                ops.scaled_sum(total, out, total, 1.0, scale)
+                ops.scaled_sum(out, out, part, scale, 0.0)
+                ops.scaled_sum(running, part, total if i + 1 == len(self.members) else running, 1.0, 1.0)
         return total

@@ -145,8 +145,10 @@ def window_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, eps: 
     return (heads * torch.sigmoid(h @ w["g"].T)) @ w["o"].T
 
 
-def retention(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, eps: float) -> torch.Tensor:
-    """Per head a matrix S that decays by a fixed factor and takes k v^T at every token; read with q; no softmax."""
+def retention(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, eps: float, cancellations: Optional[list] = None) -> torch.Tensor:
+    """Per head a matrix S that decays by a fixed factor and takes k v^T at every token; read with q; no softmax.
+    ``cancellations`` receives, per token, how much of S^T q is left after cancellation (the least over the heads of
+    rms(S^T q) / rms(|S|^T |q|)): the division by the root mean square magnifies rounding where little is left."""
     L = h.shape[0]
     H, D, V = int(m["heads"]), int(m["dim"]), int(m["vdim"])
     pos = torch.arange(L)
@@ -158,9 +160,14 @@ def retention(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, eps: float) 
     decay = torch.tensor([float(d) for d in m["decay"]], dtype=h.dtype)
     S = torch.zeros(H, D, V, dtype=h.dtype)
     out = torch.zeros(L, H, V, dtype=h.dtype)
+    left_over = torch.zeros(L, dtype=h.dtype)
     for t in range(L):
         S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
         out[t] = torch.einsum("hdv,hd->hv", S, q[t])
+        spread = torch.einsum("hdv,hd->hv", S.abs(), q[t].abs())
+        left_over[t] = ((out[t] ** 2).mean(-1).sqrt() / (spread ** 2).mean(-1).sqrt().clamp_min(1e-30)).min()
+    if cancellations is not None:
+        cancellations.append(left_over)
     out = rms_norm(out, None, eps).reshape(L, H * V)
     g = h @ w["g"].T
     return (out * g * torch.sigmoid(g)) @ w["o"].T
@@ -170,9 +177,9 @@ def sub(weights: Dict[str, torch.Tensor], prefix: str) -> Dict[str, torch.Tensor
     return {n[len(prefix):]: t for n, t in weights.items() if n.startswith(prefix)}
 
 
-def side_by_side(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, eps: float) -> torch.Tensor:
+def side_by_side(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, eps: float, cancellations: Optional[list] = None) -> torch.Tensor:
     left = window_attention(h, sub(w, "left."), m["left"], eps)
-    right = retention(h, sub(w, "right."), m["right"], eps)
+    right = retention(h, sub(w, "right."), m["right"], eps, cancellations)
     return float(m["left_scale"]) * left + float(m["right_scale"]) * right
 
 
@@ -218,9 +225,12 @@ def open_walk(x: torch.Tensor, x0: torch.Tensor, w_in: torch.Tensor, step_row: t
     return torch.cat([x, x0], dim=-1) @ w_in.T + step_row
 
 
-def layer(x: torch.Tensor, w: Dict[str, torch.Tensor], spec: dict, eps: float, margins: Optional[list] = None) -> torch.Tensor:
-    mixers = {"latent_attention": latent_attention, "parallel": side_by_side}
-    x = x + mixers[spec["type"]](rms_norm(x, w["norm1"], eps), sub(w, "mix."), spec["mixer"], eps)
+def layer(x: torch.Tensor, w: Dict[str, torch.Tensor], spec: dict, eps: float, margins: Optional[list] = None,
+          cancellations: Optional[list] = None) -> torch.Tensor:
+    if spec["type"] == "parallel":
+        x = x + side_by_side(rms_norm(x, w["norm1"], eps), sub(w, "mix."), spec["mixer"], eps, cancellations)
+    else:
+        x = x + latent_attention(rms_norm(x, w["norm1"], eps), sub(w, "mix."), spec["mixer"], eps)
     if spec.get("mlp") is not None:
         x = x + moe_ff(rms_norm(x, w["norm2"], eps), sub(w, "mlp."), spec["mlp"], margins)
     return x
@@ -239,8 +249,11 @@ def walk_order(cfg: dict):
 
 
 def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float64,
-            streams: Optional[list] = None, margins: Optional[list] = None) -> torch.Tensor:
-    """Logits [L, vocab] of one whole sequence.  ``streams`` receives the stream after every layer that ran."""
+            streams: Optional[list] = None, margins: Optional[list] = None, cancellations: Optional[list] = None) -> torch.Tensor:
+    """Logits [L, vocab] of one whole sequence.  ``streams`` receives the stream after every layer that ran; ``margins``
+    receives per-token margins of every routed layer (``route_margins``: a small one marks a token at which rounding to 16
+    bits may choose other experts), ``cancellations`` what cancellation leaves of every retention's output (``retention``: a
+    small one marks a token at which rounding is magnified)."""
     w = {n: t.to(dtype) for n, t in weights.items()}
     eps = float(cfg["norm"]["eps"])
     x0 = w["embed"][torch.tensor(list(tokens))]
@@ -248,7 +261,7 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtyp
     for i, t, opens in walk_order(cfg):
         if opens:
             x = open_walk(x, x0, w["loop.in"], w["loop.step"][t])
-        x = layer(x, sub(w, f"l{i}."), cfg["layers"][i], eps, margins)
+        x = layer(x, sub(w, f"l{i}."), cfg["layers"][i], eps, margins, cancellations)
         if streams is not None:
             streams.append(x.clone())
     return rms_norm(x, w["final.norm"], eps) @ w["head"].T * float(cfg.get("logit_scale", 1.0))
