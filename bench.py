@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--shape 8b|14b|32b] [--layers L] [--batch B] [--context C] [--no-points] [--no-e2e]
-    python bench.py --design bubotar|topunex|megusun [--sizes 2k,4k] [--steps K]      (another workload: see bench_design.py)
+    python bench.py --design bubotar|topunex|megusun|bumotar [--sizes 2k,4k] [--steps K]      (another workload: see bench_design.py)
 
 A step is one decode step.  The default run has the layer sizes of the Qwen3-8B
 configuration (36 layers, hidden 4096, 32/8 heads of 128, intermediate 12288, vocabulary
@@ -312,7 +312,7 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--design", default=None, choices=["bubotar", "topunex", "megusun"],
+    ap.add_argument("--design", default=None, choices=["bubotar", "topunex", "megusun", "bumotar"],
                     help="instead of the default workload: prefill and decode of this design beside the closest existing model at equal size")
     ap.add_argument("--sizes", default="", help="with --design: sizes to run, with commas between them (default: all)")
     args = ap.parse_args()

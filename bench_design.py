@@ -1,8 +1,8 @@
 """Throughput of another design beside the closest existing model at equal size (``bench.py --design NAME``).
 
 For each size the design's model and a Qwen3 dense model of the same width, depth, heads, feed-forward size and vocabulary
-(for Megusun: a Topunex model, the closest one, with the same width, depth, projection sizes, experts and vocabulary; its
-entry keeps the key "dense") are built with random weights (bfloat16) and timed through the step function:
+(for Megusun and Bumotar: a Topunex model, the closest one, with the same width, depth, projection sizes, experts and vocabulary;
+its entry keeps the key "dense") are built with random weights (bfloat16) and timed through the step function:
 
   prefill   one step of 2,048 prompt tokens (tokens a second, ms)
   decode    steps of single tokens of 8 requests whose context ends at 2,048 (tokens a second, ms per step)
@@ -128,6 +128,88 @@ def megusun_work(z: dict, phase: str) -> Dict[str, Tuple[float, float, str]]:
         "moe_gate_up": (Lm * (n * top * 2 * fe * w * 2 + n * w * 2), Lm * 4.0 * n * top * fe * w, "fp32 FMA"),
         "moe_down": (Lm * (n * top * fe * w * 2 + n * w * 4), Lm * 2.0 * n * top * fe * w, "fp32 FMA"),
         "silu_mul": (Lm * n * fs * 6, 0.0, ""),
+    }
+    return {k: (b * steps, f * steps, on) for k, (b, f, on) in work.items()}
+
+
+# Bumotar at sizes that resemble layers of real models: six layers (parallel, latent, parallel, parallel, latent, parallel) of which
+# the second and third are walked twice, eight layer runs in all.  A parallel layer has a window attention (heads of 128, half of
+# each rotating, a cap, a window of 1,024) beside a retention (as many heads, keys of 64, values of 128); a latent layer has a latent
+# of 512 and a rotated part of 64; every layer has 32 experts of which a token uses 4, beside a gated shared expert.  The shape
+# also carries what the model beside it needs (Topunex: eight layers, kept keys, a dense first feed-forward).
+BUMOTAR_SIZES = {
+    "1k": dict(width=1024, layers=8, heads=8, kv_heads=2, dim=128, rot=64, window=1024, keep=4, ret_dim=64, ret_vdim=128, rank=512,
+               ff=4096, experts=16, top=2, expert_ff=512, shared_ff=1024, vocab=32000),
+    "2k": dict(width=2048, layers=8, heads=16, kv_heads=4, dim=128, rot=64, window=1024, keep=4, ret_dim=64, ret_vdim=128, rank=512,
+               ff=8192, experts=32, top=4, expert_ff=1024, shared_ff=2048, vocab=32000),
+    "4k": dict(width=4096, layers=8, heads=32, kv_heads=8, dim=128, rot=64, window=1024, keep=4, ret_dim=64, ret_vdim=128, rank=512,
+               ff=12288, experts=32, top=4, expert_ff=2048, shared_ff=4096, vocab=32000),
+}
+BUMOTAR_RUNS = ["parallel", "latent", "parallel", "latent", "parallel", "parallel", "latent", "parallel"]      # the eight layer runs
+
+
+def bumotar_config(z: dict) -> dict:
+    H = z["heads"]
+    left = dict(heads=H, kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["dim"], scale=1.0 / math.sqrt(z["dim"]), softcap=50.0,
+                mask=dict(size=z["window"]), rot=dict(base=500000.0, dims=z["rot"], scaling=dict(factor=8.0)))
+    right = dict(heads=H, dim=z["ret_dim"], vdim=z["ret_vdim"], decay=[1.0 - 2.0 ** (-5.0 - 5.0 * h / max(1, H - 1)) for h in range(H)],
+                 rot=dict(base=1000000.0, dims=z["ret_dim"]))
+    par = dict(type="parallel", mixer=dict(left=left, right=right, left_scale=0.6, right_scale=0.9))
+    lat = dict(type="latent_attention", mixer=dict(heads=H, dim=z["dim"], rot_dim=z["rot"], vdim=z["dim"], kv_rank=z["rank"],
+                                                   scale=1.0 / math.sqrt(z["dim"] + z["rot"]),
+                                                   rot=dict(base=250000.0, dims=z["rot"], scaling=dict(factor=2.0, original=1024, fast=32.0, slow=1.0))))
+    moe = dict(kind="moe", expert=dict(ff=z["expert_ff"]), router=dict(experts=z["experts"], top=z["top"]), shared=dict(ff=z["shared_ff"]))
+    order = [par, lat, par, par, lat, par]
+    layers = [dict(copy_of, mlp=dict(moe)) for copy_of in order]
+    return dict(architecture="Bumotar", vocab=z["vocab"], width=z["width"], norm=dict(eps=1e-6), logit_scale=1.0, layers=layers,
+                loop=dict(start=1, stop=3, times=2))
+
+
+def bumotar_work(z: dict, phase: str) -> Dict[str, Tuple[float, float, str]]:
+    """Per kernel class of Bumotar: (bytes it must move, flops, what the flops run on) summed over the layer runs of a step."""
+    n = PROMPT if phase == "prefill" else BATCH
+    seqs = 1 if phase == "prefill" else BATCH
+    start = 0 if phase == "prefill" else CONTEXT - 1
+    Lp, Ll = BUMOTAR_RUNS.count("parallel"), BUMOTAR_RUNS.count("latent")
+    L, w = Lp + Ll, z["width"]
+    H, G, d, rot, rank = z["heads"], z["kv_heads"], z["dim"], z["rot"], z["rank"]
+    D, V = z["ret_dim"], z["ret_vdim"]
+    E, top, fe, fs = z["experts"], z["top"], z["expert_ff"], z["shared_ff"]
+    steps = 1 if phase == "prefill" else 4
+    row = rank + rot
+    win_pairs = seqs * _window_pairs(n // seqs, start, z["window"], 0)
+    all_pairs = seqs * _pairs(n // seqs, start)
+    keys_read = seqs * min(start + n // seqs, z["window"] + (n // seqs if phase == "prefill" else 0))
+    window = (Lp * (keys_read * G * 2 * d * 2 + n * H * d * (4 + 2)), Lp * 4.0 * H * d * win_pairs)
+    if phase == "prefill":          # the latent layers expand their keys: heads of their own, keys d + rot wide, values d wide
+        latent = (Ll * n * H * ((d + rot) * (4 + 2) + d * 4), Ll * 2.0 * H * (2 * d + rot) * all_pairs)
+    else:                           # the absorbed form over the cached rows: keys rank + rot wide, values rank wide
+        latent = (Ll * (seqs * (start + 1) * row * 2 + n * H * (row * 4 + rank * 2)), Ll * 2.0 * H * (row + rank) * all_pairs)
+    attention = (window[0] + latent[0], window[1] + latent[1])
+    chunk = 32
+    chunks = n // chunk if phase == "prefill" else 0
+    retention = (Lp * (n * (2 * H * (D + V) * 4 + 2 * H * D * 4 * 2 + H * V * 2) + seqs * H * D * V * 8 + chunks * H * D * V * 4 * 3),
+                 Lp * n * H * (4.0 * D * V + (chunk * (D + V) if phase == "prefill" else 0.0)))
+    distinct = E * (1.0 - (1.0 - top / E) ** n)
+    work = {
+        "paged_attention_general_tc": (attention[0], attention[1], "bf16 tensor"),
+        "paged_attention_general_tiled": (attention[0], attention[1], "fp32 FMA"),
+        "paged_attention_general": (attention[0], attention[1], "fp32 FMA"),
+        "retention": (retention[0], retention[1], "fp32 FMA"),
+        "qk_prepare": (Lp * n * ((H + 2 * G) * d * 4 + H * d * 4 + 2 * G * d * 2), 0.0, ""),
+        "sigmoid_gate_strided": (Lp * n * H * d * (4 + 2 + 2) + Ll * n * H * (d * 4 + 2), 0.0, ""),
+        "scaled_sum": (Lp * n * w * (4 + 4 + 2), 0.0, ""),
+        "concat_streams": (2 * n * w * (4 + 2 + 4 + 4), 0.0, ""),
+        "add_bias": (2 * n * w * 8, 0.0, ""),
+        "heads_linear": (Ll * (2 * H * d * rank * 2 + n * H * (d * 2 + rank * 4 + rank * 2 + d * 2)), Ll * 2.0 * n * H * d * rank * 2, "fp32 FMA"),
+        "latent_prepare": (Ll * (n * H * (rot * 2 + rot * 4) + n * row * 4), 0.0, ""),
+        "latent_expand_keys": (Ll * n * H * (2 * d + rot) * 2, 0.0, ""),
+        "add_rmsnorm": ((2 * L + 1) * n * w * (4 + 4 + 2 + 2), 0.0, ""),
+        "moe_route": (L * (n * w * 2 + (E + 1) * w * 4), 0.0, ""),
+        "moe_grouped": (L * (distinct * 3 * w * fe * 2 + n * w * 4 + n * top * (fe * 4 + w * 8)), L * 2.0 * n * top * 3 * w * fe, "bf16 tensor"),
+        "moe_gate_up": (L * (n * top * 2 * fe * w * 2 + n * w * 2), L * 4.0 * n * top * fe * w, "fp32 FMA"),
+        "moe_down": (L * (n * top * fe * w * 2 + n * w * 4), L * 2.0 * n * top * fe * w, "fp32 FMA"),
+        "silu_mul": (L * n * fs * 6, 0.0, ""),
     }
     return {k: (b * steps, f * steps, on) for k, (b, f, on) in work.items()}
 
@@ -335,7 +417,8 @@ def rooflines(kernels: Dict[str, List[float]], work: Dict[str, Tuple[float, floa
 # design -> (sizes, its configuration, its kernels' work, the configuration of the model beside it, that model's kernels' work)
 DESIGNS = {"bubotar": (SIZES, bubotar_config, own_work, dense_config, like_work),
            "topunex": (TOPUNEX_SIZES, topunex_config, topunex_work, dense_config, like_work),
-           "megusun": (MEGUSUN_SIZES, megusun_config, megusun_work, topunex_config, topunex_work)}
+           "megusun": (MEGUSUN_SIZES, megusun_config, megusun_work, topunex_config, topunex_work),
+           "bumotar": (BUMOTAR_SIZES, bumotar_config, bumotar_work, topunex_config, topunex_work)}
 
 
 def run(args, bench) -> dict:
