@@ -24,6 +24,8 @@ namespace {
 using namespace pb;
 
 constexpr int kChunk = 32;
+constexpr int kPowers = kChunk + 4;        // room for decay^0 .. decay^kChunk, a multiple of four floats
+constexpr int kStateRows = 32;           // rows of the entering state that a block stages at a time
 
 __global__ void retention_prepare_kernel(const float* __restrict__ rows, long stride, const float* __restrict__ cos_t,
                                          const float* __restrict__ sin_t, float* __restrict__ q_out, float* __restrict__ k_out,
@@ -174,12 +176,21 @@ __global__ void retention_fold_kernel(float* __restrict__ U, const float* __rest
     const float full = powf(dec, (float)kChunk);
     float* kept = state + (size_t)state_slots[s] * state_stride + (size_t)h * DV + e;
     float S = *kept;
-    for (int c = 0; c < nc; ++c) {
-        float* u = U + ((size_t)(first + c) * H + h) * DV + e;
-        const float own = *u;
-        *u = S;
-        const int n = min(kChunk, len - c * kChunk);
-        S = fmaf(n == kChunk ? full : powf(dec, (float)n), S, own);
+    float* u0 = U + ((size_t)first * H + h) * DV + e;
+    const size_t step = (size_t)H * DV;
+    constexpr int kAhead = 8;                // chunks whose own parts are in flight together: they do not depend on the fold
+    for (int c0 = 0; c0 < nc; c0 += kAhead) {
+        float own[kAhead];
+#pragma unroll
+        for (int k = 0; k < kAhead; ++k) own[k] = c0 + k < nc ? u0[(size_t)(c0 + k) * step] : 0.0f;
+#pragma unroll
+        for (int k = 0; k < kAhead; ++k) {
+            if (c0 + k < nc) {
+                u0[(size_t)(c0 + k) * step] = S;
+                const int n = min(kChunk, len - (c0 + k) * kChunk);
+                S = fmaf(n == kChunk ? full : powf(dec, (float)n), S, own[k]);
+            }
+        }
     }
     *kept = S;
 }
@@ -192,20 +203,22 @@ __global__ void retention_chunk_out_kernel(const float* __restrict__ qr, const f
     pdl_wait();
     extern __shared__ __align__(16) float smem[];
     const int Dp = (D + 3) & ~3, Vp = (V + 3) & ~3;
-    float* qs = smem;                        // [kChunk][Dp]
-    float* ks = qs + kChunk * Dp;            // [kChunk][Dp]
-    float* vs = ks + kChunk * Dp;            // [kChunk][Vp]
+    const int Dq = Dp + 4;                   // row stride of q and k: rows a multiple of 32 floats apart would share their banks
+    float* qs = smem;                        // [kChunk][Dq]
+    float* ks = qs + kChunk * Dq;            // [kChunk][Dq]
+    float* vs = ks + kChunk * Dq;            // [kChunk][Vp]
     float* os = vs + kChunk * Vp;            // [kChunk][Vp]
     float* A = os + kChunk * Vp;             // [kChunk][kChunk]
-    float* pw = A + kChunk * kChunk;         // [kChunk + 1]: decay^m
+    float* pw = A + kChunk * kChunk;         // [kPowers]: decay^m, m <= kChunk
+    float* st = pw + kPowers;                // [kStateRows][Vp]: rows of the entering state
     const int chunk = blockIdx.x, h = blockIdx.y;
     int s, t0, t1;
     if (!find_chunk(cu_q, n_seqs, chunk, s, t0, t1)) return;
     const int n = t1 - t0;
     const float dec = decay[h];
     for (int i = threadIdx.x; i <= kChunk; i += blockDim.x) pw[i] = powf(dec, (float)i);
-    for (int i = threadIdx.x; i < kChunk * Dp; i += blockDim.x) {
-        const int j = i / Dp, d = i - j * Dp;
+    for (int i = threadIdx.x; i < kChunk * Dq; i += blockDim.x) {
+        const int j = i / Dq, d = i - j * Dq;
         const bool in = j < n && d < D;
         qs[i] = in ? qr[((size_t)(t0 + j) * H + h) * D + d] : 0.0f;
         ks[i] = in ? kr[((size_t)(t0 + j) * H + h) * D + d] : 0.0f;
@@ -219,8 +232,8 @@ __global__ void retention_chunk_out_kernel(const float* __restrict__ qr, const f
         const int i = e / kChunk, j = e - i * kChunk;
         float dot = 0.0f;
         if (j <= i && i < n) {
-            const float* a = qs + i * Dp;
-            const float* b = ks + j * Dp;
+            const float* a = qs + i * Dq;
+            const float* b = ks + j * Dq;
             for (int d = 0; d < Dp; d += 4) {
                 const float4 x = *reinterpret_cast<const float4*>(a + d), z = *reinterpret_cast<const float4*>(b + d);
                 dot = fmaf(x.x, z.x, dot); dot = fmaf(x.y, z.y, dot); dot = fmaf(x.z, z.z, dot); dot = fmaf(x.w, z.w, dot);
@@ -233,41 +246,85 @@ __global__ void retention_chunk_out_kernel(const float* __restrict__ qr, const f
     const float* Sc = S_in + ((size_t)chunk * H + h) * D * V;
     const bool vec_s = (V & 3) == 0;
     const int tiles_v = Vp >> 2, tiles = (kChunk >> 2) * tiles_v;
-    for (int tile = threadIdx.x; tile < tiles; tile += blockDim.x) {
+    // A thread owns a 4 x 4 tile of the outputs (rows i0 .., columns v ..); where there are more tiles than threads the block
+    // walks them in passes.  The entering state comes through shared memory, kStateRows rows at a time, fetched by the whole
+    // block with all its loads in flight together, so its latency is paid once per group of rows.
+    for (int pass = 0; pass * (int)blockDim.x < tiles; ++pass) {
+        const int tile = pass * blockDim.x + threadIdx.x;
         const int i0 = (tile / tiles_v) << 2, v = (tile % tiles_v) << 2;
-        if (i0 >= n) continue;
+        const bool mine = tile < tiles && i0 < n;
         float inner[4][4] = {}, carried[4][4] = {};
-        const int j_end = min(n, i0 + 4);
-        for (int j = 0; j < j_end; ++j) {
-            const float4 b = *reinterpret_cast<const float4*>(vs + j * Vp + v);
-            const float bv[4] = {b.x, b.y, b.z, b.w};
+        if (mine) {
+            // four keys at a time: eight 16-byte loads feed 64 multiply-adds.  Scores of keys behind a query and rows behind
+            // the chunk's last token are zero, so a group of four may reach past them.
+            for (int j = 0; j < i0 + 4; j += 4) {
+                float a[4][4], b[4][4];
 #pragma unroll
-            for (int x = 0; x < 4; ++x) {
-                const float a = A[(i0 + x) * kChunk + j];
+                for (int x = 0; x < 4; ++x) {
+                    const float4 t = *reinterpret_cast<const float4*>(A + (i0 + x) * kChunk + j);
+                    a[x][0] = t.x; a[x][1] = t.y; a[x][2] = t.z; a[x][3] = t.w;
+                }
 #pragma unroll
-                for (int z = 0; z < 4; ++z) inner[x][z] = fmaf(a, bv[z], inner[x][z]);
+                for (int k = 0; k < 4; ++k) {
+                    const float4 t = *reinterpret_cast<const float4*>(vs + (j + k) * Vp + v);
+                    b[k][0] = t.x; b[k][1] = t.y; b[k][2] = t.z; b[k][3] = t.w;
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+#pragma unroll
+                    for (int x = 0; x < 4; ++x)
+#pragma unroll
+                        for (int z = 0; z < 4; ++z) inner[x][z] = fmaf(a[x][k], b[k][z], inner[x][z]);
             }
         }
-        for (int d = 0; d < D; ++d) {
-            float bv[4];
-            if (vec_s) {
-                const float4 b = *reinterpret_cast<const float4*>(Sc + (size_t)d * V + v);
-                bv[0] = b.x; bv[1] = b.y; bv[2] = b.z; bv[3] = b.w;
-            } else {
-#pragma unroll
-                for (int z = 0; z < 4; ++z) bv[z] = v + z < V ? Sc[(size_t)d * V + v + z] : 0.0f;
+        for (int dt = 0; dt < D; dt += kStateRows) {
+            __syncthreads();                 // the rows staged before have been read
+            for (int i = threadIdx.x; i < kStateRows * tiles_v; i += blockDim.x) {
+                const int r = i / tiles_v, c = (i - r * tiles_v) << 2;
+                float4 t = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (dt + r < D) {
+                    const float* src = Sc + (size_t)(dt + r) * V + c;
+                    if (vec_s) {
+                        t = *reinterpret_cast<const float4*>(src);
+                    } else {
+                        t.x = src[0];
+                        if (c + 1 < V) t.y = src[1];
+                        if (c + 2 < V) t.z = src[2];
+                        if (c + 3 < V) t.w = src[3];
+                    }
+                }
+                *reinterpret_cast<float4*>(st + r * Vp + c) = t;
             }
+            __syncthreads();
+            if (mine) {
+                const int rows_here = min(kStateRows, Dp - dt);          // a multiple of four; q is zero from D on
+                for (int d = 0; d < rows_here; d += 4) {
+                    float a[4][4], b[4][4];
 #pragma unroll
-            for (int x = 0; x < 4; ++x) {
-                const float a = qs[(i0 + x) * Dp + d];
+                    for (int x = 0; x < 4; ++x) {
+                        const float4 t = *reinterpret_cast<const float4*>(qs + (i0 + x) * Dq + dt + d);
+                        a[x][0] = t.x; a[x][1] = t.y; a[x][2] = t.z; a[x][3] = t.w;
+                    }
 #pragma unroll
-                for (int z = 0; z < 4; ++z) carried[x][z] = fmaf(a, bv[z], carried[x][z]);
+                    for (int k = 0; k < 4; ++k) {
+                        const float4 t = *reinterpret_cast<const float4*>(st + (d + k) * Vp + v);
+                        b[k][0] = t.x; b[k][1] = t.y; b[k][2] = t.z; b[k][3] = t.w;
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+#pragma unroll
+                        for (int x = 0; x < 4; ++x)
+#pragma unroll
+                            for (int z = 0; z < 4; ++z) carried[x][z] = fmaf(a[x][k], b[k][z], carried[x][z]);
+                }
             }
         }
+        if (mine) {
 #pragma unroll
-        for (int x = 0; x < 4; ++x)
+            for (int x = 0; x < 4; ++x)
 #pragma unroll
-            for (int z = 0; z < 4; ++z) os[(i0 + x) * Vp + v + z] = fmaf(pw[i0 + x + 1], carried[x][z], inner[x][z]);
+                for (int z = 0; z < 4; ++z) os[(i0 + x) * Vp + v + z] = fmaf(pw[i0 + x + 1], carried[x][z], inner[x][z]);
+        }
     }
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
@@ -370,7 +427,7 @@ PB_EXPORT int pb_retention(int dtype, const float* rows, long stride, const floa
     rc = launch_pdl(retention_fold_kernel, dim3((DV + 255) / 256, H, n_seqs), dim3(256), 0, stream, U, decay, state, state_stride, cu_q,
                     state_slots, H, DV);
     if (rc != 0) return rc;
-    const size_t smem_out = sizeof(float) * (kChunk * (2 * (size_t)Dp + 2 * (size_t)Vp) + kChunk * kChunk + kChunk + 1);
+    const size_t smem_out = sizeof(float) * (kChunk * (2 * (size_t)(Dp + 4) + 2 * (size_t)Vp) + kChunk * kChunk + kPowers + kStateRows * (size_t)Vp);
     if (dtype == PB_F32) {
         rc = allow_smem(retention_chunk_out_kernel<float>, smem_out);
         if (rc != 0) return rc;
