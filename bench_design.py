@@ -150,14 +150,14 @@ BUMOTAR_RUNS = ["parallel", "latent", "parallel", "latent", "parallel", "paralle
 
 def bumotar_config(z: dict) -> dict:
     H = z["heads"]
-    left = dict(heads=H, kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["dim"], scale=1.0 / math.sqrt(z["dim"]), softcap=50.0,
-                mask=dict(size=z["window"]), rot=dict(base=500000.0, dims=z["rot"], scaling=dict(factor=8.0)))
+    left = dict(heads=H, kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["dim"], scale=1.0 / math.sqrt(z["dim"]), softcap=30.0,
+                mask=dict(size=z["window"]), rot=dict(base=100000.0, dims=z["rot"], scaling=dict(factor=4.0)))
     right = dict(heads=H, dim=z["ret_dim"], vdim=z["ret_vdim"], decay=[1.0 - 2.0 ** (-5.0 - 5.0 * h / max(1, H - 1)) for h in range(H)],
-                 rot=dict(base=1000000.0, dims=z["ret_dim"]))
-    par = dict(type="parallel", mixer=dict(left=left, right=right, left_scale=0.6, right_scale=0.9))
+                 rot=dict(base=10000.0, dims=z["ret_dim"]))
+    par = dict(type="parallel", mixer=dict(left=left, right=right, left_scale=0.5, right_scale=1.0))
     lat = dict(type="latent_attention", mixer=dict(heads=H, dim=z["dim"], rot_dim=z["rot"], vdim=z["dim"], kv_rank=z["rank"],
                                                    scale=1.0 / math.sqrt(z["dim"] + z["rot"]),
-                                                   rot=dict(base=250000.0, dims=z["rot"], scaling=dict(factor=2.0, original=1024, fast=32.0, slow=1.0))))
+                                                   rot=dict(base=10000.0, dims=z["rot"], scaling=dict(factor=4.0, original=4096, fast=32.0, slow=1.0))))
     moe = dict(kind="moe", expert=dict(ff=z["expert_ff"]), router=dict(experts=z["experts"], top=z["top"]), shared=dict(ff=z["shared_ff"]))
     order = [par, lat, par, par, lat, par]
     layers = [dict(copy_of, mlp=dict(moe)) for copy_of in order]

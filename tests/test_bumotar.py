@@ -56,7 +56,7 @@ def right(heads, dim, vdim, decay, rot=None):
     return m
 
 
-def par(l, r, left_scale=0.6, right_scale=0.9):
+def par(l, r, left_scale=0.7, right_scale=1.2):
     return dict(type="parallel", mixer=dict(left=l, right=r, left_scale=left_scale, right_scale=right_scale))
 
 
@@ -86,7 +86,7 @@ RAMP = dict(factor=4.0, original=64, fast=4.0, slow=0.5)
 # that starts at the first layer, a model without walks.
 BUMO_A = config([
     layer(par(left(4, 2, 16, 24, window=9, rot=dict(base=1000.0, dims=8, scaling=dict(factor=4.0)), softcap=20.0),
-              right(3, 8, 12, [0.9, 0.97, 0.995], rot=dict(base=50.0, dims=4)), 0.6, 0.9), moe(5, 2, 24, shared=40)),
+              right(3, 8, 12, [0.9, 0.97, 0.995], rot=dict(base=50.0, dims=4)), 0.55, 0.8), moe(5, 2, 24, shared=40)),
     layer(latent(3, 12, 6, 10, 20, base=100.0, scaling=RAMP), moe(4, 1, 32)),
     layer(par(left(3, 3, 8, 8, window=5, rot=dict(base=300.0, dims=8)), right(2, 12, 8, [0.8, 0.99], rot=dict(base=20.0, dims=12)),
               1.2, 0.5)),
@@ -100,7 +100,7 @@ BUMO_B = config([
 ], vocab=131, width=40, eps=3e-6, loop=(0, 2, 2), logit_scale=2.0)
 # head sizes at which the bfloat16 engine's prompt attention runs on the tensor cores; no walk
 BUMO_C = config([
-    layer(par(left(4, 2, 64, 64, window=40, rot=dict(base=10000.0, dims=32, scaling=dict(factor=8.0)), softcap=50.0),
+    layer(par(left(4, 2, 64, 64, window=40, rot=dict(base=10000.0, dims=32, scaling=dict(factor=6.0)), softcap=40.0),
               right(2, 32, 64, [0.98, 0.999], rot=dict(base=10000.0, dims=32))), moe(6, 2, 32, shared=48)),
     layer(latent(2, 128, 64, 128, 96, base=10000.0, scaling=dict(factor=2.0, original=64, fast=32.0, slow=1.0)), moe(4, 2, 64)),
     layer(par(left(2, 1, 128, 128, window=33, rot=dict(base=5000.0, dims=128)), right(3, 24, 40, [0.9, 0.95, 0.99]))),
@@ -141,7 +141,7 @@ def test_config_becomes_parts():
     assert [b.mixer.kind for b in spec.blocks] == ["side_by_side", "latent_attention", "side_by_side", "latent_attention"]
     assert spec.blocks[2].feed_forward is None and spec.blocks[2].feed_forward_norm is None
     (_, l0, ls), (_, r0, rs) = spec.blocks[0].mixer.option("members")
-    assert (ls, rs) == (0.6, 0.9)
+    assert (ls, rs) == (0.55, 0.8)
     assert (l0.kind, l0.window, l0.softcap, l0.fixed_sink, l0.output_gate, l0.qk_norm_eps, l0.qk_norm_weight) == \
         ("attention", 9, 20.0, 0.0, True, 1e-5, True)
     assert (l0.position.rotary_dim, l0.position.divide, l0.position.ramp, l0.position.magnitude) == (8, 4.0, None, 1.0)
@@ -205,7 +205,7 @@ def test_config_errors(edit, match):
 def test_rotary_frequencies_of_the_engine_and_of_the_plain_model_agree():
     from pulsar_b200.config.specs import PositionSpec
     from pulsar_b200.parts.rope import RotaryEmbedding
-    for rot in (dict(base=100.0, dims=6, scaling=RAMP), dict(base=250000.0, dims=16, scaling=dict(factor=2.0, original=1024, fast=32.0, slow=1.0)),
+    for rot in (dict(base=100.0, dims=6, scaling=RAMP), dict(base=40000.0, dims=24, scaling=dict(factor=3.0, original=512, fast=16.0, slow=2.0)),
                 dict(base=1000.0, dims=8, scaling=dict(factor=4.0)), dict(base=50.0, dims=4), dict(base=7.0, dims=10, scaling=dict(
                     factor=3.0, original=9, fast=0.01, slow=0.001))):
         freqs, magnitude = plain.frequencies_of(rot)
